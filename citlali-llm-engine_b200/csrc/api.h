@@ -1,0 +1,63 @@
+// The C interface of the kernel library.  Every function launches on the given stream and
+// returns 0, a cudaError_t (> 0), or a refusal (< 0) whose text citlali_last_error() gives.
+// dtype codes: 0 = float32, 1 = bfloat16.  All sizes are in elements unless named bytes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* citlali_last_error(void);
+
+// out[m, :] = table[tokens[m], :] widened to float32.
+int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
+                       int rows, int hidden, int vocab, int32_t* error_flag, cudaStream_t stream);
+
+// out[r, :] = x[idx[r], :] * rsqrt(mean(x^2) + eps) * gain   (idx may be null: identity).
+int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,
+                     void* out, int out_dtype, int rows, int hidden, float eps, cudaStream_t stream);
+
+// act[m, i] = silu(gate) * up, gate/up taken from one [rows, 2*inter] matrix whose columns
+// alternate in runs of `run`: gate run, up run, gate run, ...
+int citlali_swiglu(const void* gate_up, void* act, int dtype, int rows, int inter, int run,
+                   cudaStream_t stream);
+
+// y[M, N] = x[M, K] . w[N, K]^T on CUDA cores with float accumulation, k ascending.
+// accumulate != 0: y (float32) += product.
+int citlali_gemm_simt(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype,
+                      int M, int N, int K, int accumulate, cudaStream_t stream);
+
+// In place on a [rows, (nq + 2 nkv) d] projection: per-head RMSNorm of q and k, half-split
+// rotation by the row's position, then k and v written to the paged cache of the row's slot.
+// write_cache == 0 leaves the cache alone (a layer that reads another layer's cache).
+int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
+                               const float* inv_freq, int rotary_dim,
+                               const int32_t* row_slot, const int32_t* row_pos,
+                               const int32_t* page_table, int page_table_stride,
+                               void* k_pool, void* v_pool, int cache_dtype, int page_size,
+                               int rows, int nq, int nkv, int head_dim, float eps, int write_cache,
+                               cudaStream_t stream);
+
+// Causal attention of every row over the cache of its slot: keys lo..pos, lo = 0 or
+// pos - window + 1.  One order of operations for prompts and for single tokens.
+int citlali_attention_rows(const void* q, int q_stride, int dtype,
+                           const void* k_pool, const void* v_pool, int cache_dtype,
+                           const int32_t* page_table, int page_table_stride,
+                           const int32_t* row_slot, const int32_t* row_pos,
+                           void* out, int out_stride, int rows, int nq, int nkv, int head_dim,
+                           int page_size, int window, int max_keys, float scale,
+                           cudaStream_t stream);
+
+// tokens[r] = argmax of logits[r, :] over finite values, lowest index on ties.
+int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int vocab, cudaStream_t stream);
+
+// tokens[r] = first index whose inclusive CDF of softmax(logits[r] / temperature[r]) exceeds
+// uniform[r]; temperature[r] <= 0 means argmax.
+int citlali_sample_rows(const float* logits, const float* temperature, const float* uniform,
+                        int32_t* tokens, int rows, int vocab, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

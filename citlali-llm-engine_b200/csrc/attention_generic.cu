@@ -1,0 +1,230 @@
+// The attention mixer's generic kernels: q/k head norm + rotation + cache write, and
+// attention of every row over its slot's cached keys.  They take any head size up to 256,
+// any number of heads and groups, any page size; they serve the true 32-bit path and are
+// the bfloat16 path's kernels where the tensor-core ones refuse a shape.
+#include "api.h"
+#include "common.cuh"
+
+namespace citlali {
+
+constexpr int kMaxPairsPerLane = 4;   // head_dim <= 256: 128 rotation pairs over 32 lanes
+
+// One warp per (row, head).  Heads 0..nq-1 are queries, then nkv key heads, then nkv value
+// heads, as they lie in the fused projection's output row.
+//   q, k: RMSNorm over the head with a gain shared by all heads (rms_norm_heads_kernel,
+//         kernels.cu:95-124), then the half-split rotation by the row's position with
+//         angle = float(pos) * inv_freq[i] (rope_kernel, kernels.cu:485-521; inv_freq[i] =
+//         theta^(-2i/d) is tabulated by the host).  No rounding between the two.
+//   k, v: stored at the row's position in the slot's pages (store_kv_kernel,
+//         kernels.cu:524-533), k after norm and rotation, v as projected.
+template <typename T, typename TG>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
+                          const float* __restrict__ inv_freq,
+                          const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                          const int32_t* __restrict__ page_table, int page_table_stride,
+                          T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
+                          int nq, int nkv, int d, float eps, int write_cache) {
+    const int row = blockIdx.x;
+    const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int total = nq + 2 * nkv;
+    if (head >= total) return;
+    const int half = d >> 1;
+    T* src = qkv + ((size_t)row * total + head) * d;
+    const int pos = row_pos[row];
+
+    size_t cache_off = 0;
+    if (head >= nq && write_cache) {
+        const int g = (head - nq) % nkv;
+        const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
+        cache_off = (((size_t)page * nkv + g) * page_size + (pos % page_size)) * d;
+    }
+
+    if (head >= nq + nkv) {   // a value head: a copy into the cache
+        if (!write_cache) return;
+        for (int i = lane; i < d; i += 32) v_pool[cache_off + i] = src[i];
+        return;
+    }
+
+    const TG* gain = head < nq ? q_gain : k_gain;
+    float x0[kMaxPairsPerLane], x1[kMaxPairsPerLane];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxPairsPerLane; ++j) {
+        const int i = lane + 32 * j;
+        x0[j] = x1[j] = 0.0f;
+        if (i < half) {
+            x0[j] = ldf(src, i);
+            x1[j] = ldf(src, i + half);
+            ss = fmaf(x0[j], x0[j], ss);
+            ss = fmaf(x1[j], x1[j], ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = gain ? rsqrtf(ss / (float)d + eps) : 1.0f;
+    T* dst = head < nq ? src : (k_pool + cache_off);
+    const bool store = head < nq || write_cache;
+#pragma unroll
+    for (int j = 0; j < kMaxPairsPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            float a = x0[j], b = x1[j];
+            if (gain) {
+                a = a * inv * ldf(gain, i);
+                b = b * inv * ldf(gain, i + half);
+            }
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            if (store) {
+                stf(dst, i, a * c - b * s);
+                stf(dst, i + half, a * s + b * c);
+            }
+        }
+    }
+}
+
+// One block per (row, query head).  Query head j reads KV head j / (nq / nkv)
+// (attention_scores_kernel, kernels.cu:564-565).  Keys lo..pos of the row's slot:
+//   s_t = (q . k_t) * scale;  m = max s_t;  e_t = exp(s_t - m);  Z = sum e_t;
+//   o_i = sum_t (e_t / Z) v_t[i]   with the division per term, t ascending
+// (attention_values_kernel, kernels.cu:605-649).  Every reduction's order is a function of
+// the number of keys alone, so a row's result does not depend on the step it came in.
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool,
+                      const T* __restrict__ v_pool, const int32_t* __restrict__ page_table,
+                      int page_table_stride, const int32_t* __restrict__ row_slot,
+                      const int32_t* __restrict__ row_pos, T* __restrict__ out, int out_stride,
+                      int nq, int nkv, int d, int page_size, int window, float scale) {
+    extern __shared__ float smem[];
+    __shared__ float scratch[32];
+    const int row = blockIdx.x, head = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = head / (nq / nkv);
+    const int pos = row_pos[row];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n = pos - lo + 1;
+    float* qs = smem;          // d
+    float* sc = smem + d;      // n
+    const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
+
+    const T* qrow = q + (size_t)row * q_stride + (size_t)head * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) qs[i] = ldf(qrow, i);
+    __syncthreads();
+
+    for (int t = warp; t < n; t += 4) {
+        const int key = lo + t;
+        const T* krow = k_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * d;
+        float s = 0.0f;
+        for (int i = lane; i < d; i += 32) s = fmaf(qs[i], ldf(krow, i), s);
+        s = warp_sum(s);
+        if (lane == 0) sc[t] = s * scale;
+    }
+    __syncthreads();
+
+    float m = -INFINITY;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) m = fmaxf(m, sc[t]);
+    m = block_max(m, scratch);
+    float z = 0.0f;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+        const float e = expf(sc[t] - m);
+        sc[t] = e;
+        z += e;
+    }
+    z = block_sum(z, scratch);
+    for (int t = threadIdx.x; t < n; t += blockDim.x) sc[t] = sc[t] / z;
+    __syncthreads();
+
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int t = 0; t < n; ++t) {
+            const int key = lo + t;
+            const T* vrow = v_pool + (((size_t)pages[key / page_size] * nkv + g) * page_size + key % page_size) * d;
+            acc = fmaf(sc[t], ldf(vrow, i), acc);
+        }
+        stf(out, (size_t)row * out_stride + (size_t)head * d + i, acc);
+    }
+}
+
+}  // namespace citlali
+
+using namespace citlali;
+
+extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
+                                          const float* inv_freq, int rotary_dim,
+                                          const int32_t* row_slot, const int32_t* row_pos,
+                                          const int32_t* page_table, int page_table_stride,
+                                          void* k_pool, void* v_pool, int cache_dtype, int page_size,
+                                          int rows, int nq, int nkv, int head_dim, float eps, int write_cache,
+                                          cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (head_dim <= 0 || head_dim % 2 != 0 || head_dim > 64 * kMaxPairsPerLane) {
+        set_last_error("qk_norm_rope_cache: head size %d must be even and at most %d", head_dim, 64 * kMaxPairsPerLane);
+        return kBadShape;
+    }
+    if (rotary_dim != head_dim) {
+        set_last_error("qk_norm_rope_cache: rotating %d of %d head elements is not implemented (whole head only)",
+                       rotary_dim, head_dim);
+        return kBadShape;
+    }
+    if (cache_dtype != dtype) {
+        set_last_error("qk_norm_rope_cache: the cache's dtype must equal the activations'");
+        return kBadDType;
+    }
+    if (nq <= 0 || nkv < 0 || page_size <= 0) {
+        set_last_error("qk_norm_rope_cache: bad head counts (%d, %d) or page size %d", nq, nkv, page_size);
+        return kBadShape;
+    }
+    const int total = nq + 2 * nkv;
+    dim3 grid(rows, (total + 3) / 4);
+    if (grid.y > 65535) {
+        set_last_error("qk_norm_rope_cache: too many heads (%d)", total);
+        return kTooLarge;
+    }
+    return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
+        return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
+            qk_norm_rope_cache_kernel<T, TG><<<grid, 128, 0, stream>>>(
+                (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, row_slot, row_pos, page_table,
+                page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache);
+            return CITLALI_LAUNCH_CHECK();
+        });
+    });
+}
+
+extern "C" int citlali_attention_rows(const void* q, int q_stride, int dtype,
+                                      const void* k_pool, const void* v_pool, int cache_dtype,
+                                      const int32_t* page_table, int page_table_stride,
+                                      const int32_t* row_slot, const int32_t* row_pos,
+                                      void* out, int out_stride, int rows, int nq, int nkv, int head_dim,
+                                      int page_size, int window, int max_keys, float scale,
+                                      cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (cache_dtype != dtype) {
+        set_last_error("attention_rows: the cache's dtype must equal the activations'");
+        return kBadDType;
+    }
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || head_dim <= 0 || nq > 65535) {
+        set_last_error("attention_rows: %d query heads do not group over %d key/value heads (head size %d)",
+                       nq, nkv, head_dim);
+        return kBadShape;
+    }
+    const size_t smem = (size_t)(head_dim + max_keys) * sizeof(float);
+    if (smem > 200 * 1024) {
+        set_last_error("attention_rows: %d keys for one row need %zu bytes of shared memory, more than 204800",
+                       max_keys, smem);
+        return kTooLarge;
+    }
+    return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
+        auto kernel = attention_rows_kernel<T>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        dim3 grid(rows, nq);
+        kernel<<<grid, 128, smem, stream>>>((const T*)q, q_stride, (const T*)k_pool, (const T*)v_pool, page_table,
+                                             page_table_stride, row_slot, row_pos, (T*)out, out_stride, nq, nkv,
+                                             head_dim, page_size, window, scale);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}

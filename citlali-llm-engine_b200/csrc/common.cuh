@@ -1,0 +1,77 @@
+// Shared device helpers: storage types, widening loads, rounding stores, block reductions.
+//
+// Every kernel widens what it reads to float, computes in float and rounds once at the
+// store, as the reference's kernels do with half (src/compute/cuda/kernels.cu:13-24);
+// storage here is bfloat16 or float.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace citlali {
+
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Error codes a launcher returns (0 = launched).  Negative values are refusals made on the
+// host before any launch; positive values are cudaError_t.
+enum Refusal : int {
+    kOk = 0,
+    kBadDType = -1,
+    kBadShape = -2,
+    kTooLarge = -3,
+    kBadAlignment = -4,
+    kNoDriverEntry = -5,
+};
+
+void set_last_error(const char* fmt, ...);
+
+__device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stf(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block whose size is a multiple of 32 (at most 1024); every thread gets the
+// result.  `scratch` holds 32 floats.  The order of additions is fixed by the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.0f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+}  // namespace citlali
+
+// Dispatch on a runtime dtype code to a template argument.
+#define CITLALI_DISPATCH_FLOAT(code, T, ...)                                   \
+    [&]() -> int {                                                             \
+        if ((code) == citlali::kF32) { using T = float; return __VA_ARGS__(); }          \
+        if ((code) == citlali::kBF16) { using T = __nv_bfloat16; return __VA_ARGS__(); } \
+        citlali::set_last_error("dtype code %d is neither float32 (0) nor bfloat16 (1)", (int)(code)); \
+        return (int)citlali::kBadDType;                                        \
+    }()
+
+#define CITLALI_LAUNCH_CHECK() (int)cudaGetLastError()

@@ -1,0 +1,109 @@
+// Row-wise kernels: embedding gather, RMSNorm, the SiLU gate.  One implementation serves
+// the 32-bit path and the bfloat16 path; only storage types differ.
+#include "api.h"
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+
+namespace citlali {
+
+static thread_local char g_last_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+}
+
+// x = E[token], a row copy with no scaling (reference: embed_kernel, kernels.cu:27-35).
+// A token outside the vocabulary is not read: the row is zeroed and the flag is raised.
+template <typename TW>
+__global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* __restrict__ tokens,
+                                  float* __restrict__ out, int hidden, int vocab, int32_t* error_flag) {
+    const int row = blockIdx.x;
+    const int tok = tokens[row];
+    const bool ok = tok >= 0 && tok < vocab;
+    if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+    const TW* src = table + (size_t)(ok ? tok : 0) * hidden;
+    float* dst = out + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ldf(src, i) : 0.0f;
+}
+
+// inv = rsqrt(sum x^2 / n + eps); y = x * inv * gain (reference: rms_norm_kernel,
+// kernels.cu:73-92, which runs one block per vector; here one block per row).
+template <typename TG, typename TO>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
+                                const int32_t* __restrict__ row_index, TO* __restrict__ out,
+                                int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[row] : row) * hidden;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    TO* dst = out + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) stf(dst, i, src[i] * inv * ldf(gain, i));
+}
+
+// act = g / (1 + exp(-g)) * u (reference: swiglu_kernel, kernels.cu:474-482).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int inter, int run) {
+    const int row = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const size_t base = (size_t)row * 2 * inter + (size_t)(i / run) * 2 * run + (i % run);
+    const float g = ldf(gate_up, base);
+    const float u = ldf(gate_up, base + run);
+    stf(act, (size_t)row * inter + i, g / (1.0f + expf(-g)) * u);
+}
+
+}  // namespace citlali
+
+using namespace citlali;
+
+extern "C" const char* citlali_last_error(void) { return g_last_error; }
+
+extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
+                                  int rows, int hidden, int vocab, int32_t* error_flag, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    return CITLALI_DISPATCH_FLOAT(table_dtype, TW, [&] {
+        embed_rows_kernel<TW><<<rows, 256, 0, stream>>>((const TW*)table, tokens, out, hidden, vocab, error_flag);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}
+
+extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,
+                                void* out, int out_dtype, int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
+        return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
+            rms_norm_kernel<TG, TO><<<rows, threads, 0, stream>>>(x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
+            return CITLALI_LAUNCH_CHECK();
+        });
+    });
+}
+
+extern "C" int citlali_swiglu(const void* gate_up, void* act, int dtype, int rows, int inter, int run,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (run <= 0 || inter % run != 0) {
+        set_last_error("swiglu: gate/up run %d does not divide the intermediate size %d", run, inter);
+        return kBadShape;
+    }
+    if ((inter + 255) / 256 > 65535) {
+        set_last_error("swiglu: intermediate size %d exceeds the grid limit", inter);
+        return kTooLarge;
+    }
+    return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
+        dim3 grid(rows, (inter + 255) / 256);
+        swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)gate_up, (T*)act, inter, run);
+        return CITLALI_LAUNCH_CHECK();
+    });
+}

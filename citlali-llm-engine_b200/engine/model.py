@@ -1,0 +1,111 @@
+"""A decoder built from a ModelSpec: embedding, the schedule of layers, final norm, head.
+
+The forward pass follows QwenModel::forward_token (src/model/qwen_model.cpp:239-419) for a
+batch of rows instead of one token: embedding rows, each scheduled layer on all rows, and
+only for the rows whose logits are wanted the final norm and the output matrix (the
+reference skips both for prompt tokens that are not the last, :378-380).  Which layers
+exist, what they are made of, and in which order they run is the spec's data.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import ModelSpec
+from ..errors import require
+from ..parts.base import BuildContext, StepBatch, part_class
+from ..parts.linear import DenseLinear
+from ..weights.loader import TensorSpec, WeightHandle
+
+
+def _build_layers(spec: ModelSpec):
+    return [part_class("block", l.block)(l) for l in spec.layers]
+
+
+def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
+    """Every checkpoint tensor the model reads, in a fixed order.  No device is touched."""
+    specs = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size), "matrix")]
+    for block in _build_layers(spec):
+        specs.extend(block.tensor_specs())
+    norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix)
+    specs.extend(norm.tensor_specs())
+    # tied: the head is the embedding and a stored head is ignored; undecided: used if present
+    specs.append(TensorSpec(spec.head_name, (spec.vocab_size, spec.hidden_size), "matrix",
+                            optional=spec.tie_head_to_embedding is not False))
+    seen = set()
+    for s in specs:
+        require(s.name not in seen, f"two parts of the model claim the tensor '{s.name}'")
+        seen.add(s.name)
+    return specs
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, ctx: BuildContext):
+        spec.validate()
+        self.spec = spec
+        self.ctx = ctx
+        self.layers = _build_layers(spec)
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix)
+        self.head = DenseLinear([spec.head_name], [spec.vocab_size], spec.hidden_size)
+        self.embedding: Optional[torch.Tensor] = None
+        self.tied = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return expected_tensors(self.spec)
+
+    def cache_requirements(self) -> List[object]:
+        """Per schedule step: what it keeps (None for a step that keeps nothing or reads
+        another step's cache)."""
+        out = []
+        for step in self.spec.schedule:
+            out.append(None if step.cache_of is not None else self.layers[step.layer].cache_requirement())
+        return out
+
+    def bind(self, weights: Dict[str, WeightHandle]) -> None:
+        ctx, spec = self.ctx, self.spec
+        emb = weights[spec.embedding_name].tensor
+        require(tuple(emb.shape) == (spec.vocab_size, spec.hidden_size),
+                f"unexpected tensor shape for {spec.embedding_name}: got {list(emb.shape)}, "
+                f"expected {[spec.vocab_size, spec.hidden_size]}")
+        self.embedding = emb.to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        for block in self.layers:
+            block.bind(weights, ctx)
+        self.final_norm.bind(weights, ctx)
+        tie = spec.tie_head_to_embedding
+        if tie is None:
+            tie = spec.head_name not in weights      # absent head: reuse the embedding (qwen_model.cpp:71-75)
+        self.tied = bool(tie)
+        if self.tied:
+            self.head.bind_shared(self.embedding, ctx.dtype)
+        else:
+            require(spec.head_name in weights, f"missing required tensor: {spec.head_name}")
+            self.head.bind(weights, ctx)
+
+    def weight_bytes_read_per_step(self) -> int:
+        """Bytes of weights one step reads when each matrix it uses is read once (embedding rows
+        and norm gains are left out: they are thousands of times smaller)."""
+        total = self.head.nbytes
+        for step in self.spec.schedule:
+            block = self.layers[step.layer]
+            for part in block.parts():
+                for lin in vars(part).values():
+                    if isinstance(lin, DenseLinear):
+                        total += lin.nbytes
+        return total
+
+    def forward(self, batch: StepBatch, cache) -> torch.Tensor:
+        """Logits ``[wanted, vocab]`` float32 for ``batch.want_rows``, in that order."""
+        ctx, spec = self.ctx, self.spec
+        x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
+        ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag)
+        for i, step in enumerate(spec.schedule):
+            source = i if step.cache_of is None else step.cache_of
+            view = cache.view(source) if cache.has_view(source) else None
+            self.layers[step.layer].forward(x, batch, view, write_cache=step.cache_of is None)
+        wanted = int(batch.want_rows.numel())
+        if wanted == 0:
+            return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=ctx.device)
+        h = self.final_norm.forward(x, row_index=batch.want_rows)
+        return self.head.forward(h, out_dtype=torch.float32)

@@ -1,0 +1,174 @@
+"""Python face of the kernel library: one function per kernel, taking torch tensors.
+
+Each function checks dtypes, shapes and contiguity, then calls the C entry point on the
+current CUDA stream.  There is no CPU implementation and no library implementation behind
+these functions: if the kernel library cannot be built or loaded, or a tensor is not on a
+CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .errors import CitlaliError, require
+
+_F32, _BF16 = 0, 1
+_lib = None
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise CitlaliError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        from .csrc.build import load
+        l = load()
+        l.citlali_last_error.restype = ctypes.c_char_p
+        _lib = l
+    return _lib
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code < 0:
+        raise CitlaliError(f"{what} refused: {lib().citlali_last_error().decode()}")
+    raise CitlaliError(f"{what}: CUDA error {code} at launch")
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None:
+            require(t.is_cuda, "kernels run on a CUDA device only; a tensor on the CPU was given")
+            require(t.is_contiguous(), "kernels take contiguous tensors")
+
+
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor):
+    _need_cuda(table, tokens, out, error_flag)
+    require(tokens.dtype == torch.int32 and out.dtype == torch.float32, "embed_rows: tokens int32, out float32")
+    rows, hidden = out.shape
+    require(table.shape[1] == hidden and tokens.numel() == rows, "embed_rows: shapes do not fit")
+    _check(lib().citlali_embed_rows(_ptr(table), _i(_dtype_code(table)), _ptr(tokens), _ptr(out), _i(rows),
+                                    _i(hidden), _i(table.shape[0]), _ptr(error_flag), _stream()), "embed_rows")
+
+
+def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+             row_index: Optional[torch.Tensor] = None):
+    _need_cuda(x, gain, out, row_index)
+    require(x.dtype == torch.float32, "rms_norm: the input rows are float32")
+    rows, hidden = out.shape
+    require(x.shape[1] == hidden and gain.numel() == hidden, "rms_norm: shapes do not fit")
+    if row_index is not None:
+        require(row_index.dtype == torch.int32 and row_index.numel() == rows, "rms_norm: bad row index")
+    else:
+        require(x.shape[0] == rows, "rms_norm: shapes do not fit")
+    _check(lib().citlali_rms_norm(_ptr(x), _ptr(gain), _i(_dtype_code(gain)), _ptr(row_index), _ptr(out),
+                                  _i(_dtype_code(out)), _i(rows), _i(hidden), _f(eps), _stream()), "rms_norm")
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor, run: int):
+    _need_cuda(gate_up, act)
+    rows, inter = act.shape
+    require(gate_up.shape == (rows, 2 * inter) and gate_up.dtype == act.dtype, "swiglu: shapes or dtypes do not fit")
+    _check(lib().citlali_swiglu(_ptr(gate_up), _ptr(act), _i(_dtype_code(act)), _i(rows), _i(inter), _i(run),
+                                _stream()), "swiglu")
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool = False):
+    _need_cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    require(w.shape[1] == K and y.shape == (M, N), "gemm_simt: shapes do not fit")
+    _check(lib().citlali_gemm_simt(_ptr(x), _i(_dtype_code(x)), _ptr(w), _i(_dtype_code(w)), _ptr(y),
+                                   _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(1 if accumulate else 0), _stream()),
+           "gemm_simt")
+
+
+def qk_norm_rope_cache(qkv, q_gain, k_gain, inv_freq, rotary_dim, row_slot, row_pos, page_table,
+                       k_pool, v_pool, page_size, nq, nkv, head_dim, eps, write_cache=True):
+    _need_cuda(qkv, q_gain, k_gain, inv_freq, row_slot, row_pos, page_table, k_pool, v_pool)
+    rows = qkv.shape[0]
+    require(qkv.shape[1] == (nq + 2 * nkv) * head_dim, "qk_norm_rope_cache: the projection's width does not fit")
+    require(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+            "qk_norm_rope_cache: bad frequency table")
+    require(row_slot.dtype == torch.int32 and row_pos.dtype == torch.int32 and page_table.dtype == torch.int32,
+            "qk_norm_rope_cache: index tensors are int32")
+    gain_code = _dtype_code(q_gain) if q_gain is not None else _F32
+    if q_gain is not None and k_gain is not None:
+        require(q_gain.dtype == k_gain.dtype, "qk_norm_rope_cache: q and k gains differ in dtype")
+    cache_code = _dtype_code(k_pool) if k_pool is not None else _dtype_code(qkv)
+    _check(lib().citlali_qk_norm_rope_cache(
+        _ptr(qkv), _i(_dtype_code(qkv)), _ptr(q_gain), _ptr(k_gain), _i(gain_code), _ptr(inv_freq), _i(rotary_dim),
+        _ptr(row_slot), _ptr(row_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(k_pool), _ptr(v_pool),
+        _i(cache_code), _i(page_size), _i(rows), _i(nq), _i(nkv), _i(head_dim), _f(eps),
+        _i(1 if write_cache else 0), _stream()), "qk_norm_rope_cache")
+
+
+def attention_rows(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos, out, nq, nkv, head_dim,
+                   page_size, window, max_keys, scale):
+    _need_cuda(k_pool, v_pool, page_table, row_slot, row_pos, out)
+    require(q.is_cuda, "kernels run on a CUDA device only")
+    rows = out.shape[0]
+    _check(lib().citlali_attention_rows(
+        _ptr(q), _i(q_stride), _i(_dtype_code(q)), _ptr(k_pool), _ptr(v_pool), _i(_dtype_code(k_pool)),
+        _ptr(page_table), _i(page_table.shape[1]), _ptr(row_slot), _ptr(row_pos), _ptr(out), _i(out.shape[1]),
+        _i(rows), _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(max_keys), _f(scale),
+        _stream()), "attention_rows")
+
+
+def argmax_rows(logits: torch.Tensor, tokens: torch.Tensor):
+    _need_cuda(logits, tokens)
+    require(logits.dtype == torch.float32 and tokens.dtype == torch.int32, "argmax_rows: float32 in, int32 out")
+    rows, vocab = logits.shape
+    _check(lib().citlali_argmax_rows(_ptr(logits), _ptr(tokens), _i(rows), _i(vocab), _stream()), "argmax_rows")
+
+
+def sample_rows(logits, temperature, uniform, tokens):
+    _need_cuda(logits, temperature, uniform, tokens)
+    require(logits.dtype == torch.float32 and tokens.dtype == torch.int32 and temperature.dtype == torch.float32
+            and uniform.dtype == torch.float32, "sample_rows: float32 in, int32 out")
+    rows, vocab = logits.shape
+    require(temperature.numel() >= rows and uniform.numel() >= rows and tokens.numel() >= rows,
+            "sample_rows: per-row tensors are too short")
+    _check(lib().citlali_sample_rows(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(tokens), _i(rows),
+                                     _i(vocab), _stream()), "sample_rows")
+
+
+# ---- choices between kernels ---------------------------------------------------------------
+
+def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, scale):
+    """Attention of every row of the step over its slot's cache.  ``q`` holds the rotated
+    queries with ``q_stride`` elements between rows."""
+    attention_rows(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table,
+                   batch.row_slot, batch.row_pos, out, nq, nkv, head_dim, cache_view.page_size,
+                   window, batch.max_keys, scale)
+
+
+def gemm_tc_accepts(x, w, y) -> bool:
+    return False
+
+
+def gemm_tc(x, w, y, accumulate=False):
+    raise CitlaliError("the tensor-core product is not built")

@@ -1,0 +1,107 @@
+"""Causal grouped-query attention over the cache, with optional per-head q/k RMSNorm.
+
+The order of operations is the reference's (src/model/qwen_model.cpp:315-351): q, k, v
+projections without bias; RMSNorm over each q and k head with a gain [head_dim] shared by all
+heads and the layer norms' eps, before the rotation; v untouched; k and v stored at the
+token's position; query head j reads KV head j // (heads / kv_heads); scores scaled by
+1/sqrt(head_dim); keys 0..p for the token at position p (no window in the reference; a
+window is a parameter here); softmax and value sum in 32-bit; output projection added to the
+residual stream.
+
+Parameters: hidden_size, num_heads, num_kv_heads, head_dim, qk_norm_eps (None: no head norm),
+position ({"kind": ..., ...}), window (None: all keys), kv_projection (False: the layer has no
+k/v matrices and only reads another layer's cache).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from ..cache import KVRequirement
+from ..errors import require
+from ..weights.loader import TensorSpec
+from .base import part_class, register_part
+from .linear import DenseLinear
+
+
+class GQAttention:
+    def __init__(self, params, prefix: str):
+        self.hidden = int(params["hidden_size"])
+        self.nq = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.d = int(params["head_dim"])
+        self.eps = params.get("qk_norm_eps")
+        self.window = params.get("window")
+        self.kv_projection = bool(params.get("kv_projection", True))
+        require(self.nq % self.nkv == 0,
+                f"{prefix}: {self.nq} query heads are not a multiple of {self.nkv} key/value heads")
+        require(self.d % 2 == 0, f"{prefix}: head size {self.d} must be even")
+        require(self.window is None or int(self.window) > 0, f"{prefix}: window must be positive or None")
+        pos = dict(params.get("position") or {"kind": "none"})
+        self.position = part_class("position", pos.pop("kind"))(pos, self.d)
+        self.prefix = prefix
+        names = [f"{prefix}.q_proj.weight"]
+        outs = [self.nq * self.d]
+        if self.kv_projection:
+            names += [f"{prefix}.k_proj.weight", f"{prefix}.v_proj.weight"]
+            outs += [self.nkv * self.d, self.nkv * self.d]
+        self.qkv = DenseLinear(names, outs, self.hidden)
+        self.o = DenseLinear([f"{prefix}.o_proj.weight"], [self.hidden], self.nq * self.d)
+        self.q_gain = self.k_gain = None
+
+    # ---- what it needs ---------------------------------------------------------------
+    def tensor_specs(self):
+        specs = self.qkv.tensor_specs() + self.o.tensor_specs()
+        if self.eps is not None:
+            specs.append(TensorSpec(f"{self.prefix}.q_norm.weight", (self.d,), "gain"))
+            if self.kv_projection:
+                specs.append(TensorSpec(f"{self.prefix}.k_norm.weight", (self.d,), "gain"))
+        return specs
+
+    def cache_requirement(self):
+        if not self.kv_projection:
+            return None
+        return KVRequirement(self.nkv, self.d, None if self.window is None else int(self.window))
+
+    def bind(self, weights, ctx):
+        self.qkv.bind(weights, ctx)
+        self.o.bind(weights, ctx)
+        if self.eps is not None:
+            def gain(name):
+                g = weights[name].tensor
+                require(tuple(g.shape) == (self.d,),
+                        f"unexpected tensor shape for {name}: got {list(g.shape)}, expected {[self.d]}")
+                return g.to(device=ctx.device, dtype=torch.float32 if ctx.is_float32 else g.dtype).contiguous()
+            self.q_gain = gain(f"{self.prefix}.q_norm.weight")
+            self.k_gain = gain(f"{self.prefix}.k_norm.weight") if self.kv_projection else self.q_gain
+            if self.k_gain.dtype != self.q_gain.dtype:
+                self.k_gain = self.k_gain.to(torch.float32)
+                self.q_gain = self.q_gain.to(torch.float32)
+        require(self.position.inv_freq is not None, f"{self.prefix}: this position encoding needs apply()")
+        self.inv_freq = self.position.inv_freq.to(ctx.device)
+        self.dtype = ctx.dtype
+
+    # ---- one step ----------------------------------------------------------------------
+    def forward(self, h, batch, cache_view, residual, write_cache=True):
+        require(cache_view is not None, f"{self.prefix}: attention needs a key/value cache")
+        req = cache_view.requirement
+        nkv_here = self.nkv if self.kv_projection else 0
+        require(req.head_dim == self.d and req.num_kv_heads == self.nkv,
+                f"{self.prefix}: the cache holds {req.num_kv_heads} heads of {req.head_dim}, "
+                f"the layer has {self.nkv} of {self.d}")
+        qkv = self.qkv.forward(h)
+        ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.inv_freq, self.position.rotary_dim,
+                               batch.row_slot, batch.row_pos, cache_view.page_table,
+                               cache_view.keys, cache_view.values, cache_view.page_size,
+                               self.nq, nkv_here, self.d, float(self.eps or 0.0),
+                               write_cache=write_cache and self.kv_projection)
+        out = torch.empty((batch.rows, self.nq * self.d), dtype=self.dtype, device=h.device)
+        ops.attention(qkv, qkv.shape[1], cache_view, batch, out, self.nq, self.nkv, self.d,
+                      int(self.window or 0), 1.0 / math.sqrt(self.d))
+        self.o.forward(out, accumulate_into=residual)
+        return residual
+
+
+register_part("mixer", "gqa_attention", GQAttention)

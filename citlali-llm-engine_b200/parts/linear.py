@@ -1,0 +1,86 @@
+"""Dense linear maps: y = x . W^T with W stored [out, in] row-major, no bias.
+
+The reference routes every projection through ``LinearBackend::forward(weight, input,
+output)`` (include/citlali/model/linear_backend.h:10-21), which picks a kernel from the
+weight's storage (src/model/linear_backend.cpp:17-68).  This is the same seam: model parts
+call :class:`DenseLinear`; it picks the kernel from the compute dtype and the shape.
+
+* float32: the CUDA-core product (k ascending, one chain per output element).
+* bfloat16: the tensor-core product where its shape rules hold (inner size a multiple of 8,
+  16-byte aligned rows), else the CUDA-core product on bfloat16 storage.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..errors import require
+from ..weights.loader import TensorSpec
+
+
+class DenseLinear:
+    def __init__(self, names: Sequence[str], out_features: Sequence[int], in_features: int,
+                 interleave_run: Optional[int] = None):
+        """One matrix, or several with the same input stacked along the output axis (``names``
+        in order).  ``interleave_run``: for exactly two stacked matrices, alternate runs of that
+        many rows of the first and of the second (gate and up of a gated feed-forward)."""
+        self.names = list(names)
+        self.out_splits = list(out_features)
+        self.in_features = in_features
+        self.out_features = sum(out_features)
+        self.interleave_run = interleave_run
+        if interleave_run is not None:
+            require(len(self.names) == 2 and out_features[0] == out_features[1]
+                    and out_features[0] % interleave_run == 0,
+                    "interleaving needs two matrices of equal height that the run divides")
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(n, (o, self.in_features), "matrix") for n, o in zip(self.names, self.out_splits)]
+
+    def bind(self, weights, ctx):
+        mats = [weights[n].tensor for n in self.names]
+        for n, m, o in zip(self.names, mats, self.out_splits):
+            require(tuple(m.shape) == (o, self.in_features),
+                    f"unexpected tensor shape for {n}: got {list(m.shape)}, expected {[o, self.in_features]}")
+        mats = [m.to(device=ctx.device, dtype=ctx.dtype) for m in mats]
+        if self.interleave_run is not None:
+            r = self.interleave_run
+            a = mats[0].view(-1, r, self.in_features)
+            b = mats[1].view(-1, r, self.in_features)
+            w = torch.stack([a, b], dim=1).reshape(self.out_features, self.in_features)
+        elif len(mats) == 1:
+            w = mats[0]
+        else:
+            w = torch.cat(mats, dim=0)
+        self.weight = w.contiguous()
+        self.dtype = ctx.dtype
+
+    def bind_shared(self, weight: torch.Tensor, dtype):
+        """Use a matrix another part already holds (a head tied to the embedding)."""
+        require(tuple(weight.shape) == (self.out_features, self.in_features), "shared matrix has the wrong shape")
+        self.weight = weight
+        self.dtype = dtype
+
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``accumulate_into`` (float32 [rows, out]) receives ``+= x . W^T`` and is returned;
+        otherwise a new tensor of ``out_dtype`` (default: the compute dtype)."""
+        rows = x.shape[0]
+        if accumulate_into is not None:
+            y = accumulate_into
+        else:
+            y = torch.empty((rows, self.out_features), dtype=out_dtype or self.dtype, device=x.device)
+        if rows == 0:
+            return y
+        if self.dtype == torch.bfloat16 and ops.gemm_tc_accepts(x, self.weight, y):
+            ops.gemm_tc(x, self.weight, y, accumulate=accumulate_into is not None)
+        else:
+            ops.gemm_simt(x, self.weight, y, accumulate=accumulate_into is not None)
+        return y
+
+    @property
+    def nbytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
