@@ -1,0 +1,116 @@
+"""Generation through the entry points (Python and command line) against the plain loop."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import citlali_b200 as cb
+import plain_qwen3 as plain
+from helpers import TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def margin_ok(logits, token, need):
+    """Is `token` the plain argmax by more than `need`?"""
+    top2 = torch.topk(logits, 2).values
+    return int(torch.argmax(logits)) == token and float(top2[0] - top2[1]) > need
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lengths,steps", [("A", [5, 11, 17], 8), ("B", [1, 7, 23, 40], 12)])
+def test_greedy_generation_matches_the_plain_loop(model_dirs, name, lengths, steps, dtype):
+    stored = "float32" if dtype == "float32" else "bfloat16"
+    cfg, w = plain.load_folder(model_dirs[(name, stored)])
+    prompts = [random_tokens(cfg["vocab_size"], n, 7 + n) for n in lengths]
+    session = cb.InferenceSession().load_model(model_dirs[(name, stored)], max_context=128, dtype=dtype, max_batch=4)
+    streamed = []
+    results = session.generate(prompts, cb.GenerationOptions(max_new_tokens=steps, max_context=128),
+                               on_token=lambda r, t: streamed.append((r, t)))
+    need = 1e-4 if dtype == "float32" else 0.05
+    for r, (prompt, res) in enumerate(zip(prompts, results)):
+        assert res.generated_tokens == steps == len(res.tokens) and res.stop_reason == cb.StopReason.MAX_NEW_TOKENS
+        seq = list(prompt)
+        for t in res.tokens:
+            logits = plain.model_logits(cfg, w, seq)[-1]
+            if not margin_ok(logits, int(torch.argmax(logits)), need * float(logits.abs().max())):
+                break                      # a near tie: rounding may pick either, what follows differs
+            assert t == int(torch.argmax(logits)), f"request {r}: token {len(seq) - len(prompt)} differs"
+            seq.append(t)
+        assert [t for rr, t in streamed if rr == r] == res.tokens
+    assert session.cache.slots.free_count == 4 and session.cache.pages_held() == 0
+    # one request alone gives the same tokens as in the batch
+    alone = session.generate([prompts[1]], cb.GenerationOptions(max_new_tokens=steps, max_context=128))
+    assert alone[0].tokens == results[1].tokens
+
+
+def test_stop_tokens_early_finishers_and_many_batches(model_dirs):
+    cfg, w = plain.load_folder(model_dirs[("C", "float32")])
+    session = cb.InferenceSession().load_model(model_dirs[("C", "float32")], max_context=64, dtype="float32", max_batch=2)
+    prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (3, 9, 4, 30, 6)]
+    free = session.generate(prompts, cb.GenerationOptions(max_new_tokens=10, max_context=64, stop_ids=[]))
+    assert all(r.generated_tokens == 10 for r in free)
+    stop = free[1].tokens[4]
+    res = session.generate(prompts, cb.GenerationOptions(max_new_tokens=10, max_context=64, stop_ids=[stop]))
+    for f, r in zip(free, res):
+        if stop in f.tokens:
+            k = f.tokens.index(stop)
+            assert r.tokens == f.tokens[:k] and r.stop_reason == cb.StopReason.EOS and r.generated_tokens == k
+        else:
+            assert r.tokens == f.tokens and r.stop_reason == cb.StopReason.MAX_NEW_TOKENS
+    assert res[1].stop_reason == cb.StopReason.EOS
+    # config C names eos ids 5 and 9: they are the default stop set
+    assert session.model.spec.stop_token_ids == (5, 9)
+    limited = session.generate([prompts[3]], cb.GenerationOptions(max_new_tokens=50, max_context=40, stop_ids=[]))
+    assert limited[0].stop_reason == cb.StopReason.CONTEXT_LIMIT and limited[0].generated_tokens == 10
+    assert limited[0].tokens == free[3].tokens
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_follows_the_plain_cdf(model_dirs, dtype):
+    stored = "float32" if dtype == "float32" else "bfloat16"
+    cfg, w = plain.load_folder(model_dirs[("B", stored)])
+    prompts = [random_tokens(cfg["vocab_size"], n, 90 + n) for n in (1, 7, 23, 40)]
+    session = cb.InferenceSession().load_model(model_dirs[("B", stored)], max_context=128, dtype=dtype, max_batch=4)
+    opts = cb.GenerationOptions(max_new_tokens=12, max_context=128, temperature=0.8, seed=1234, stop_ids=[])
+    res = session.generate(prompts, opts)
+    again = session.generate(prompts, opts)
+    assert [r.tokens for r in res] == [r.tokens for r in again]                     # a fixed seed repeats
+    other = session.generate(prompts, cb.GenerationOptions(max_new_tokens=12, max_context=128, temperature=0.8,
+                                                           seed=99, stop_ids=[]))
+    assert [r.tokens for r in res] != [r.tokens for r in other]
+    alone = session.generate(prompts[2:3], opts)                                     # request index 0 now
+    slack = 1e-5 if dtype == "float32" else 3e-2
+    for r, (prompt, out) in enumerate(zip(prompts, res)):
+        seq = list(prompt)
+        for k, t in enumerate(out.tokens):
+            cdf = plain.temperature_cdf(plain.model_logits(cfg, w, seq)[-1], 0.8)
+            u = cb.uniform(1234, r, k)
+            lo = float(cdf[t - 1]) if t > 0 else 0.0
+            assert lo - slack <= u <= float(cdf[t]) + slack, f"request {r} token {k}: u={u} outside [{lo}, {float(cdf[t])}]"
+            seq.append(t)
+    assert len(alone[0].tokens) == 12
+
+
+def test_command_line(model_dirs, tmp_path):
+    cli = os.path.join(ROOT, "bin", "citlali_cli")
+    model = model_dirs[("A", "float32")]
+    prompts = [[1, 2, 3, 4, 5], [9, 8, 7]]
+    out = subprocess.run([sys.executable, cli, "--model", model, "--prompt-ids", "1,2,3,4,5", "--prompt-ids", "9,8,7",
+                          "--max-new-tokens", "6", "--ctx", "64", "--dtype", "float32", "--json"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    data = json.loads(out.stdout)
+    session = cb.InferenceSession().load_model(model, max_context=64, dtype="float32", max_batch=8)
+    want = session.generate(prompts, cb.GenerationOptions(max_new_tokens=6, max_context=64))
+    assert [r["tokens"] for r in data["results"]] == [r.tokens for r in want]
+    assert all(r["stop_reason"] == "max_new_tokens" for r in data["results"])
+    assert "[stats] tokens=12" in out.stderr and "stop=max_new_tokens,max_new_tokens" in out.stderr
+    info = subprocess.run([sys.executable, cli, "--model", model, "--info"], capture_output=True, text=True, timeout=120)
+    assert info.returncode == 0 and "hidden_size: 64" in info.stdout and "vocab_size: 512" in info.stdout
+    bad = subprocess.run([sys.executable, cli, "--model", model, "--frobnicate"], capture_output=True, text=True, timeout=120)
+    assert bad.returncode == 1 and "unknown argument: --frobnicate" in bad.stderr

@@ -1,0 +1,285 @@
+"""Each kernel alone against the plain implementation, at sizes the engine's models do not use,
+with inputs made so that a fault shows (a far key among hundreds, a window's edge, shuffled
+cache pages, ties and non-finite logits)."""
+import math
+import random
+
+import pytest
+import torch
+
+import citlali_b200 as cb
+import plain_qwen3 as plain
+from citlali_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 2 ** -8
+
+
+def close(got, want, dtype, scale=None):
+    want = want.double()
+    scale = float(want.abs().max()) if scale is None else scale
+    err = float((got.double().cpu() - want.cpu()).abs().max())
+    assert err <= tol(dtype) * max(scale, 1e-30), f"|diff| {err:.3e} against scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 130, 17), (70, 65, 100), (129, 7, 333), (64, 64, 16)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_simt(M, N, K, dtype):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(dtype); w = torch.randn(N, K, generator=g).to(dtype)
+    want = x.double() @ w.double().t()
+    y = torch.empty(M, N, dtype=dtype, device=DEV)
+    ops.gemm_simt(x.to(DEV), w.to(DEV), y)
+    close(y, want, dtype)
+    y32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_simt(x.to(DEV), w.to(DEV), y32)
+    close(y32, want, torch.float32, scale=float(want.abs().max()) * (1 if dtype == torch.float32 else 1))
+    base = torch.randn(M, N, generator=g)
+    acc = base.clone().to(DEV)
+    ops.gemm_simt(x.to(DEV), w.to(DEV), acc, accumulate=True)
+    close(acc, base.double() + want, torch.float32)
+    with pytest.raises(cb.CitlaliError, match="float32 output"):
+        ops.gemm_simt(x.to(DEV), w.to(DEV), y.to(torch.bfloat16), accumulate=True)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(77, 200, generator=g).to(DEV); w = torch.randn(90, 200, generator=g).to(DEV)
+    full = torch.empty(77, 90, device=DEV); ops.gemm_simt(x, w, full)
+    one = torch.empty(1, 90, device=DEV); ops.gemm_simt(x[40:41].contiguous(), w, one)
+    assert torch.equal(full[40:41], one)
+
+
+@pytest.mark.parametrize("hidden", [1, 100, 777, 4104])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("gain_dtype", DTYPES)
+def test_rms_norm(hidden, dtype, gain_dtype):
+    g = torch.Generator().manual_seed(hidden)
+    x = torch.randn(9, hidden, generator=g) * 3
+    gain = (1 + 0.3 * torch.randn(hidden, generator=g)).to(gain_dtype)
+    eps = 1e-3
+    out = torch.empty(9, hidden, dtype=dtype, device=DEV)
+    ops.rms_norm(x.to(DEV), gain.to(DEV), eps, out)
+    close(out, plain.rms_norm(x.double(), gain.double(), eps), dtype)
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    ops.rms_norm(x.to(DEV), gain.to(DEV), eps, out, idx.to(DEV))
+    close(out, plain.rms_norm(x.double()[idx.long()], gain.double(), eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows_and_the_fault_word(dtype):
+    table = torch.randn(50, 24).to(dtype)
+    toks = torch.tensor([3, 49, 0, 3], dtype=torch.int32)
+    out = torch.empty(4, 24, device=DEV)
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.embed_rows(table.to(DEV), toks.to(DEV), out, flag)
+    assert torch.equal(out.cpu(), plain.embedding(table, toks.tolist()).float()) and flag.tolist() == [0, 0, 0, 0]
+    ops.embed_rows(table.to(DEV), torch.tensor([1, 50, -1, 2], dtype=torch.int32, device=DEV), out, flag)
+    assert flag[0].item() == 1 and float(out[1].abs().sum()) == 0.0 and float(out[0].abs().sum()) > 0
+
+
+@pytest.mark.parametrize("inter,run", [(48, 16), (50, 50), (160, 16), (7, 1)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(inter, run, dtype):
+    g = torch.Generator().manual_seed(inter)
+    gate = (torch.randn(5, inter, generator=g) * 3).to(dtype); up = torch.randn(5, inter, generator=g).to(dtype)
+    packed = torch.stack([gate.view(5, -1, run), up.view(5, -1, run)], dim=2).reshape(5, 2 * inter)
+    act = torch.empty(5, inter, dtype=dtype, device=DEV)
+    ops.swiglu(packed.to(DEV).contiguous(), act, run)
+    close(act, plain.swiglu(gate.double(), up.double()), dtype)
+    with pytest.raises(cb.CitlaliError, match="does not divide"):
+        ops.swiglu(packed.to(DEV).contiguous(), act, 3 if inter % 3 else 11)
+
+
+def make_paged(k, v, lengths, page_size, dtype, slots_of=None, extra_pages=3, seed=0):
+    """Lay per-sequence keys/values [T, nkv, d] out in shuffled pages.  Returns pools, table."""
+    nkv, d = k[0].shape[1], k[0].shape[2]
+    need = [(n + page_size - 1) // page_size for n in lengths]
+    total = sum(need) + extra_pages
+    order = list(range(total)); random.Random(seed).shuffle(order)
+    slots_of = slots_of or list(range(len(lengths)))
+    table = torch.zeros(max(slots_of) + 1, max(need) + 1, dtype=torch.int32)
+    kp = torch.randn(total, nkv, page_size, d).mul(50).to(dtype)      # junk where nothing was written
+    vp = torch.randn(total, nkv, page_size, d).mul(50).to(dtype)
+    nxt = 0
+    for s, n, ks, vs in zip(slots_of, lengths, k, v):
+        for i in range((n + page_size - 1) // page_size):
+            page = order[nxt]; nxt += 1
+            table[s, i] = page
+            lo, hi = i * page_size, min(n, (i + 1) * page_size)
+            kp[page, :, :hi - lo] = ks[lo:hi].transpose(0, 1).to(dtype)
+            vp[page, :, :hi - lo] = vs[lo:hi].transpose(0, 1).to(dtype)
+    return kp, vp, table
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 64), (6, 3, 48, 8), (5, 5, 80, 64), (8, 1, 128, 16), (2, 2, 256, 64)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_norm_rope_cache(nq, nkv, d, page, dtype):
+    g = torch.Generator().manual_seed(d)
+    lengths = [70, 3]                      # rows: sequence 0 brings positions 66..69, sequence 1 positions 0..2
+    slots = [2, 0]
+    rows_pos = [66, 67, 68, 69, 0, 1, 2]
+    rows_slot = [2, 2, 2, 2, 0, 0, 0]
+    M = len(rows_pos)
+    qkv = torch.randn(M, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qg = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype); kg = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype)
+    theta, eps = 1e4, 1e-5
+    i = torch.arange(d // 2, dtype=torch.float64)
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2 * i / d).float()
+    empty = [torch.zeros(n, nkv, d) for n in lengths]
+    kp, vp, table = make_paged(empty, empty, lengths, page, dtype, slots_of=slots)
+    kp, vp = kp.to(DEV), vp.to(DEV)
+    before_k = kp.clone()
+    dev = qkv.to(DEV).clone()
+    ops.qk_norm_rope_cache(dev, qg.to(DEV), kg.to(DEV), inv_freq.to(DEV), d, torch.tensor(rows_slot, dtype=torch.int32, device=DEV),
+                           torch.tensor(rows_pos, dtype=torch.int32, device=DEV), table.to(DEV), kp, vp, page, nq, nkv, d, eps)
+    x = qkv.double()
+    q = x[:, :nq * d].view(M, nq, d); k = x[:, nq * d:(nq + nkv) * d].view(M, nkv, d); v = x[:, (nq + nkv) * d:].view(M, nkv, d)
+    q_want = plain.rotary_half_split(plain.head_rms_norm(q, qg.double(), eps), rows_pos, theta)
+    k_want = plain.rotary_half_split(plain.head_rms_norm(k, kg.double(), eps), rows_pos, theta)
+    close(dev[:, :nq * d].view(M, nq, d), q_want, dtype)
+    touched = torch.zeros_like(kp, dtype=torch.bool)
+    for r in range(M):
+        pg = table[rows_slot[r], rows_pos[r] // page].item(); off = rows_pos[r] % page
+        close(kp[pg, :, off], k_want[r], dtype, scale=float(k_want.abs().max()))
+        assert torch.equal(vp[pg, :, off].cpu(), v[r].to(dtype))          # values are copied as they are
+        touched[pg, :, off] = True
+    assert torch.equal(kp[~touched], before_k[~touched])                  # nothing else was written
+    # a layer that reads another layer's cache writes nothing
+    kp2 = before_k.clone()
+    ops.qk_norm_rope_cache(qkv.to(DEV).clone(), qg.to(DEV), kg.to(DEV), inv_freq.to(DEV), d,
+                           torch.tensor(rows_slot, dtype=torch.int32, device=DEV), torch.tensor(rows_pos, dtype=torch.int32, device=DEV),
+                           table.to(DEV), kp2, vp, page, nq, nkv, d, eps, write_cache=False)
+    assert torch.equal(kp2, before_k)
+
+
+def test_head_sizes_are_taken_or_refused():
+    with pytest.raises(cb.CitlaliError, match="head size"):
+        z = torch.zeros(1, 3 * 258, device=DEV)
+        t = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.qk_norm_rope_cache(z, None, None, torch.zeros(129, device=DEV), 258, t, t, torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                               torch.zeros(1, 1, 64, 258, device=DEV), torch.zeros(1, 1, 64, 258, device=DEV), 64, 1, 1, 258, 1e-6)
+
+
+def run_attention(q, k, v, past, n_new, nq, nkv, d, page, window, dtype, seed=0):
+    """q: list of [n_new_b, nq, d]; k, v: list of [past_b + n_new_b, nkv, d] already final."""
+    lengths = [p + n for p, n in zip(past, n_new)]
+    kp, vp, table = make_paged(k, v, lengths, page, dtype, seed=seed)
+    rows_slot, rows_pos = [], []
+    for b, (p, n) in enumerate(zip(past, n_new)):
+        rows_slot += [b] * n; rows_pos += list(range(p, p + n))
+    qq = torch.cat([x.reshape(x.shape[0], nq * d) for x in q]).to(dtype)
+    pad = torch.randn(qq.shape[0], 5).to(dtype)                      # queries lie inside a wider row
+    qrow = torch.cat([qq, pad], dim=1).contiguous().to(DEV)
+    out = torch.empty(qq.shape[0], nq * d, dtype=dtype, device=DEV)
+    ops.attention_rows(qrow, qrow.shape[1], kp.to(DEV), vp.to(DEV), table.to(DEV),
+                       torch.tensor(rows_slot, dtype=torch.int32, device=DEV), torch.tensor(rows_pos, dtype=torch.int32, device=DEV),
+                       out, nq, nkv, d, page, window, max(lengths), 1.0 / math.sqrt(d))
+    return out.view(-1, nq, d)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 64), (6, 3, 48, 8), (3, 1, 80, 64), (8, 2, 128, 64)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_rows_prompts_and_single_tokens(nq, nkv, d, page, dtype):
+    g = torch.Generator().manual_seed(nq * d)
+    past, n_new = [0, 130, 5], [37, 1, 64]
+    k = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    v = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    qfull = [(torch.randn(p + n, nq, d, generator=g) * 2).to(dtype).double() for p, n in zip(past, n_new)]
+    got = run_attention([qf[p:] for qf, p in zip(qfull, past)], k, v, past, n_new, nq, nkv, d, page, 0, dtype)
+    r = 0
+    for b in range(3):
+        want = plain.causal_attention(qfull[b], k[b], v[b], nq, nkv)[past[b]:]
+        close(got[r:r + n_new[b]], want, dtype)
+        r += n_new[b]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_among_hundreds(dtype):
+    """Random keys make attention nearly uniform and one missing key invisible.  Here key 3 of
+    700 lines up with the query (score about 40 above the rest) and carries a value nothing else
+    has: the output must be that value."""
+    nq, nkv, d, page = 2, 1, 32, 64
+    T = 700
+    g = torch.Generator().manual_seed(1)
+    k = torch.randn(T, nkv, d, generator=g) * 0.1
+    v = torch.randn(T, nkv, d, generator=g)
+    q = torch.zeros(1, nq, d); q[0, :, 0] = 16.0
+    k[3, 0, 0] = 16.0                                    # q.k / sqrt(32) = 45
+    v[3, 0] = torch.arange(d, dtype=torch.float32) - 7
+    k, v, q = k.to(dtype).double(), v.to(dtype).double(), q.to(dtype).double()
+    got = run_attention([q], [k], [v], [T - 1], [1], nq, nkv, d, page, 0, dtype)
+    want = plain.causal_attention(torch.cat([torch.zeros(T - 1, nq, d, dtype=torch.float64), q]), k, v, nq, nkv)[-1:]
+    close(got, want, dtype)
+    assert (got[0, 0].cpu().double() - v[3, 0]).abs().max() < 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(dtype):
+    """With a window of 5 the key at p-4 is the oldest one seen.  The key at p-5 would win every
+    score if it were seen, so seeing it by mistake shows."""
+    nq, nkv, d, page, W = 2, 2, 16, 8, 5
+    T = 40
+    g = torch.Generator().manual_seed(2)
+    k = torch.randn(T, nkv, d, generator=g) * 0.1; v = torch.randn(T, nkv, d, generator=g)
+    q = torch.randn(T, nq, d, generator=g) * 0.1
+    p = T - 1
+    q[p, :, 1] = 12.0
+    k[p - W, :, 1] = 12.0; v[p - W] = 100.0              # just outside the window
+    k[p - W + 1, :, 1] = 6.0                             # just inside
+    k, v, q = k.to(dtype).double(), v.to(dtype).double(), q.to(dtype).double()
+    want = plain.causal_attention(q, k, v, nq, nkv, window=W)
+    got = run_attention([q[10:]], [k], [v], [10], [T - 10], nq, nkv, d, page, W, dtype)
+    close(got, want[10:], dtype)
+    assert float(got[-1].abs().max()) < 10.0             # the value 100 stayed out
+    wide = run_attention([q[10:]], [k], [v], [10], [T - 10], nq, nkv, d, page, 0, dtype)
+    assert float(wide[-1].abs().max()) > 50.0            # without a window it is seen
+
+
+def test_argmax_rows_rules():
+    V = 1000
+    logits = torch.randn(6, V)
+    logits[0, 17] = 9.0; logits[0, 400] = 9.0                           # a tie: the lowest index
+    logits[1, :] = float("nan")                                        # nothing finite: id 0
+    logits[2, 5] = float("inf"); logits[2, 6] = float("nan"); logits[2, 999] = 50.0
+    logits[3, 0] = 99.0
+    logits[4, :] = -3.0                                                 # all equal
+    tok = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(logits.to(DEV), tok)
+    assert tok.tolist() == [plain.greedy(r) for r in logits] and tok.tolist()[:5] == [17, 0, 999, 0, 0]
+    big = torch.randn(3, 151936)
+    tok = torch.zeros(3, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(big.to(DEV), tok)
+    assert tok.tolist() == big.argmax(dim=1).tolist()
+
+
+@pytest.mark.parametrize("V", [7, 1000, 4097, 151936])
+def test_sample_rows_follows_the_cdf(V):
+    g = torch.Generator().manual_seed(V)
+    rows = 64
+    logits = torch.randn(rows, V, generator=g) * 3
+    logits[0, V // 2] = float("-inf"); logits[1, 0] = float("nan")
+    temps = torch.full((rows,), 0.7); temps[5] = 0.0; temps[6] = 1.5
+    us = torch.rand(rows, generator=g); us[2] = 0.0; us[3] = 0.99999994
+    tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), temps.to(DEV), us.to(DEV), tok)
+    tok = tok.tolist()
+    assert tok[5] == plain.greedy(logits[5])
+    for r in range(rows):
+        if r == 5:
+            continue
+        cdf = plain.temperature_cdf(logits[r], float(temps[r]))
+        u = float(us[r])
+        want = plain.temperature_sample(logits[r], float(temps[r]), u)
+        if tok[r] != want:
+            # 32-bit sums put the CDF's steps a few 1e-6 away from the exact ones: u must lie that close
+            lo = float(cdf[tok[r] - 1]) if tok[r] > 0 else 0.0
+            hi = float(cdf[tok[r]])
+            assert lo - 2e-5 <= u <= hi + 2e-5 and hi > lo, f"row {r}: token {tok[r]}, exact {want}, u {u}"
+        assert math.isfinite(float(logits[r, tok[r]]))

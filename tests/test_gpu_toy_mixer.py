@@ -1,0 +1,145 @@
+"""A mixer with state of its own, an architecture that uses it, and a schedule that names a
+layer twice and lets a layer read another layer's cache: all defined here, registered, built
+from a model folder and stepped, without touching the library's files."""
+import dataclasses
+import json
+
+import pytest
+import torch
+
+import citlali_b200 as cb
+import plain_qwen3 as plain
+import replay
+from citlali_b200.cache import StateRequirement
+from citlali_b200.parts.linear import DenseLinear
+
+pytestmark = pytest.mark.gpu
+
+
+class RunningMeanMixer:
+    """out_t = W . mean(h_0 .. h_t).  Per sequence it keeps the running sum and the count: a
+    state of fixed size, in the cache's state region, carried from step to step."""
+
+    def __init__(self, params, prefix):
+        self.hidden = params["hidden_size"]
+        self.proj = DenseLinear([f"{prefix}.proj.weight"], [self.hidden], self.hidden)
+
+    def tensor_specs(self):
+        return self.proj.tensor_specs()
+
+    def cache_requirement(self):
+        return StateRequirement((self.hidden + 1,), torch.float32)
+
+    def bind(self, weights, ctx):
+        self.proj.bind(weights, ctx)
+        self.dtype = ctx.dtype
+
+    def forward(self, h, batch, cache_view, residual, write_cache=True):
+        means = torch.empty(h.shape, dtype=torch.float32, device=h.device)
+        for b, slot in enumerate(batch.slots):
+            state = cache_view.storage[slot]
+            lo = sum(batch.n_new[:b])
+            for r in range(lo, lo + batch.n_new[b]):          # rows of a sequence in order
+                state[:-1] += h[r].float()
+                state[-1] += 1.0
+                means[r] = state[:-1] / state[-1]
+        self.proj.forward(means.to(self.dtype), accumulate_into=residual)
+        return residual
+
+
+@dataclasses.dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int
+    hidden_size: int
+    max_position_embeddings: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["vocab_size"], d["hidden_size"], d["max_position_embeddings"])
+
+    def to_dict(self):
+        return {"architectures": ["ToyMeanForCausalLM"], **dataclasses.asdict(self)}
+
+    def to_model_spec(self):
+        H = self.hidden_size
+        norm = lambda p: cb.PartSpec("rms_norm", {"size": H, "eps": 1e-5}, p)
+        ff = lambda p: cb.PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 2 * H}, p)
+        attn = {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qk_norm_eps": 1e-5,
+                "position": {"kind": "rotary_half_split", "theta": 1e4, "rotary_dim": 16}, "window": None}
+        layers = (
+            cb.LayerSpec("pre_norm_residual", cb.PartSpec("running_mean", {"hidden_size": H}, "l0.mix"),
+                         ff("l0.mlp"), norm("l0.n1"), norm("l0.n2")),
+            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", attn, "l1.attn"),
+                         ff("l1.mlp"), norm("l1.n1"), norm("l1.n2")),
+            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", dict(attn, kv_projection=False), "l2.attn"),
+                         ff("l2.mlp"), norm("l2.n1"), norm("l2.n2")),
+        )
+        # layer 0 runs twice (two states of its own); layer 2 has no keys and reads layer 1's
+        schedule = (cb.ScheduleStep(0), cb.ScheduleStep(1), cb.ScheduleStep(0), cb.ScheduleStep(2, cache_of=1))
+        return cb.ModelSpec("ToyMeanForCausalLM", self.vocab_size, H, self.max_position_embeddings, "emb.weight",
+                            layers, schedule, norm("final"), "head.weight", False)
+
+
+def plain_toy(w, tokens):
+    T = len(tokens)
+    x = plain.embedding(w["emb.weight"], tokens)
+    pos = list(range(T))
+
+    def mean_layer(x):
+        h = plain.rms_norm(x, w["l0.n1.weight"], 1e-5)
+        means = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+        x = x + plain.linear(means, w["l0.mix.proj.weight"])
+        return x + plain.feed_forward(plain.rms_norm(x, w["l0.n2.weight"], 1e-5), w, "l0.mlp")
+
+    x = mean_layer(x)
+    h = plain.rms_norm(x, w["l1.n1.weight"], 1e-5)
+    q = plain.linear(h, w["l1.attn.q_proj.weight"]).view(T, 4, 16)
+    k = plain.linear(h, w["l1.attn.k_proj.weight"]).view(T, 2, 16)
+    v = plain.linear(h, w["l1.attn.v_proj.weight"]).view(T, 2, 16)
+    q = plain.rotary_half_split(plain.head_rms_norm(q, w["l1.attn.q_norm.weight"], 1e-5), pos, 1e4)
+    k = plain.rotary_half_split(plain.head_rms_norm(k, w["l1.attn.k_norm.weight"], 1e-5), pos, 1e4)
+    x = x + plain.linear(plain.causal_attention(q, k, v, 4, 2).reshape(T, 64), w["l1.attn.o_proj.weight"])
+    x = x + plain.feed_forward(plain.rms_norm(x, w["l1.n2.weight"], 1e-5), w, "l1.mlp")
+    x = mean_layer(x)
+    h = plain.rms_norm(x, w["l2.n1.weight"], 1e-5)
+    q2 = plain.linear(h, w["l2.attn.q_proj.weight"]).view(T, 4, 16)
+    q2 = plain.rotary_half_split(plain.head_rms_norm(q2, w["l2.attn.q_norm.weight"], 1e-5), pos, 1e4)
+    x = x + plain.linear(plain.causal_attention(q2, k, v, 4, 2).reshape(T, 64), w["l2.attn.o_proj.weight"])
+    x = x + plain.feed_forward(plain.rms_norm(x, w["l2.n2.weight"], 1e-5), w, "l2.mlp")
+    return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["head.weight"])
+
+
+@pytest.fixture
+def toy_registered():
+    cb.register_part("mixer", "running_mean", RunningMeanMixer)
+    cb.register_architecture("ToyMeanForCausalLM", ToyConfig)
+    yield
+    cb.unregister_part("mixer", "running_mean")
+    cb.unregister_architecture("ToyMeanForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(toy_registered, tmp_path, dtype):
+    cfg = ToyConfig(vocab_size=300, hidden_size=64, max_position_embeddings=256)
+    folder = cb.write_random_model(str(tmp_path / "toy"), cfg, seed=3, dtype=dtype)
+    assert json.load(open(f"{folder}/config.json"))["architectures"] == ["ToyMeanForCausalLM"]
+    _, w = plain.load_folder(folder)
+    session = cb.InferenceSession().load_model(folder, max_context=256, dtype=dtype, max_batch=2)
+    assert len(session.cache.state_groups) == 1 and session.cache.state_groups[0].steps == [0, 2]
+    assert len(session.cache.kv_groups) == 1 and session.cache.kv_groups[0].steps == [1]
+    import random
+    rng = random.Random(4)
+    reqs = [(f"t{i}", [rng.randrange(300) for _ in range(n)]) for i, n in enumerate([70, 9, 41])]
+    want = {rid: plain_toy(w, toks) for rid, toks in reqs}
+    tolerance = 2e-5 if dtype == "float32" else 2.5e-2
+    for steps in (replay.whole(reqs), replay.tail(reqs), replay.batched(reqs, [30, 9, 1], 2)):
+        got = replay.run_in_process(session, steps)
+        for (rid, pos), row in got.items():
+            ref = want[rid][pos]
+            assert (row.double() - ref).abs().max() <= tolerance * ref.abs().max() + 1e-6
+
+
+def test_unknown_part_kind_in_a_spec_is_an_error(tmp_path):
+    cfg = ToyConfig(vocab_size=300, hidden_size=64, max_position_embeddings=256)
+    with pytest.raises(cb.CitlaliError, match="unknown mixer kind 'running_mean'"):
+        cb.expected_tensors(cfg.to_model_spec())
