@@ -58,6 +58,18 @@ int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int voca
 int citlali_sample_rows(const float* logits, const float* temperature, const float* uniform,
                         int32_t* tokens, int rows, int vocab, cudaStream_t stream);
 
+// The tensor-core product (bfloat16 operands, float accumulation).  citlali_gemm_tc_plan tells
+// how a shape runs: whether the weights are the 128-row operand (*swapped), the narrow tile
+// (*bn), the K split (*splits) and the bytes of scratch for split-K partials.
+int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int* swapped, int* bn, int* splits,
+                         size_t* workspace_bytes);
+// y[M, N] = x[M, K] . w[N, K]^T (y_dtype 0: float32, 1: bfloat16); accumulate != 0: y (float32) +=.
+// K must be a multiple of 8 and the operands 16-byte aligned.  error_flag[1..2] receive the
+// code and block of a wait that ran out.
+int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                    int accumulate, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                    int sm_count, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

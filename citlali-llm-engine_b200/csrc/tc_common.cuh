@@ -1,0 +1,134 @@
+// Inline PTX for the Blackwell tensor-core path: mbarriers, TMA tile loads, tcgen05 MMA with
+// accumulators in tensor memory, and waits that give up after a time limit instead of hanging.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace citlali {
+namespace tc {
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // a wait that lasts 2 s has failed
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_timer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Wait for a phase of an mbarrier, but not for ever: returns false when another thread of the
+// block has given up (`*abort_flag`), or after kWaitLimitNs, in which case it records `code`
+// in error_flag[1] (and the block in error_flag[2]) and raises the block's abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* error_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer();
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 31u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer() - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (error_flag) {
+                    atomicExch(error_flag + 1, code);
+                    atomicExch(error_flag + 2, (int)blockIdx.x);
+                }
+                return false;
+            }
+            __nanosleep(64);
+        }
+    }
+}
+
+// One 2-D tile [box rows x box cols] from a row-major matrix into shared memory; completion
+// is counted in bytes on `bar`.  `c_inner` (elements along the row) must make a 16-byte
+// multiple; here it is always a multiple of 64 bfloat16.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c_inner, int c_outer, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c_inner), "r"(c_outer), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]^T, bfloat16 operands, float accumulators, one CTA.
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// When every MMA issued so far by this thread has finished, arrive once on `bar`.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive accumulator columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bfloat16),
+// 128-byte swizzle, groups of 8 rows 1024 bytes apart; the tile starts on a 1024-byte boundary
+// and `byte_offset` (a multiple of 32 below 128) selects the 16-element K slice.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t tile_addr, uint32_t byte_offset) {
+    uint64_t d = 0;
+    d |= (uint64_t)(((tile_addr + byte_offset) >> 4) & 0x3FFFu);     // start address
+    d |= (uint64_t)1 << 16;                                         // leading byte offset (unused here)
+    d |= (uint64_t)(1024 >> 4) << 32;                               // stride byte offset
+    d |= (uint64_t)1 << 46;                                         // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                                         // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+}  // namespace tc
+}  // namespace citlali

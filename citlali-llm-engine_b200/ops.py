@@ -166,9 +166,55 @@ def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, sc
                    window, batch.max_keys, scale)
 
 
+_sm_count = {}
+_workspace = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def gemm_tc_plan(M: int, N: int, K: int, device) -> dict:
+    """How the tensor-core product of this shape runs, and the scratch bytes it needs."""
+    swapped, bn, splits = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    need = ctypes.c_size_t()
+    lib().citlali_gemm_tc_plan(_i(M), _i(N), _i(K), _i(sm_count(device)), ctypes.byref(swapped), ctypes.byref(bn),
+                               ctypes.byref(splits), ctypes.byref(need))
+    return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value, "workspace_bytes": need.value}
+
+
+def _gemm_workspace(device, nbytes: int) -> torch.Tensor:
+    """One scratch buffer per device for split-K partials; it only grows.  Kernels on one stream
+    use it one after another."""
+    key = torch.device(device).index or 0
+    ws = _workspace.get(key)
+    if ws is None or ws.numel() < nbytes:
+        require(not torch.cuda.is_current_stream_capturing(),
+                "the split-K scratch buffer would have to grow during graph capture; run the step once before capturing")
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspace[key] = ws
+    return ws
+
+
 def gemm_tc_accepts(x, w, y) -> bool:
-    return False
+    """The tensor-core product's shape rules: bfloat16 operands, an inner size that is a
+    multiple of 8 (TMA needs rows of 16-byte multiples), 16-byte aligned starts."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.float32, torch.bfloat16)
+            and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.is_contiguous() and w.is_contiguous() and y.is_contiguous())
 
 
-def gemm_tc(x, w, y, accumulate=False):
-    raise CitlaliError("the tensor-core product is not built")
+def gemm_tc(x, w, y, accumulate=False, error_flag=None):
+    _need_cuda(x, w, y, error_flag)
+    require(gemm_tc_accepts(x, w, y), "gemm_tc: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
+    M, K = x.shape
+    N = w.shape[0]
+    require(w.shape[1] == K and y.shape == (M, N), "gemm_tc: shapes do not fit")
+    need = gemm_tc_plan(M, N, K, x.device)["workspace_bytes"]
+    ws = _gemm_workspace(x.device, need) if need else None
+    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K),
+                                 _i(1 if accumulate else 0), _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
+                                 _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")

@@ -36,6 +36,7 @@ class DenseLinear:
                     and out_features[0] % interleave_run == 0,
                     "interleaving needs two matrices of equal height that the run divides")
         self.weight: Optional[torch.Tensor] = None
+        self.error_flag = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         return [TensorSpec(n, (o, self.in_features), "matrix") for n, o in zip(self.names, self.out_splits)]
@@ -57,6 +58,7 @@ class DenseLinear:
             w = torch.cat(mats, dim=0)
         self.weight = w.contiguous()
         self.dtype = ctx.dtype
+        self.error_flag = ctx.error_flag
 
     def bind_shared(self, weight: torch.Tensor, dtype):
         """Use a matrix another part already holds (a head tied to the embedding)."""
@@ -76,7 +78,7 @@ class DenseLinear:
         if rows == 0:
             return y
         if self.dtype == torch.bfloat16 and ops.gemm_tc_accepts(x, self.weight, y):
-            ops.gemm_tc(x, self.weight, y, accumulate=accumulate_into is not None)
+            ops.gemm_tc(x, self.weight, y, accumulate=accumulate_into is not None, error_flag=self.error_flag)
         else:
             ops.gemm_simt(x, self.weight, y, accumulate=accumulate_into is not None)
         return y

@@ -283,3 +283,51 @@ def test_sample_rows_follows_the_cdf(V):
             hi = float(cdf[tok[r]])
             assert lo - 2e-5 <= u <= hi + 2e-5 and hi > lo, f"row {r}: token {tok[r]}, exact {want}, u {u}"
         assert math.isfinite(float(logits[r, tok[r]]))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 192, 64), (17, 1000, 96), (33, 130, 200), (64, 4096, 512),
+                                   (100, 24, 4096), (128, 256, 512), (129, 256, 128), (300, 520, 200),
+                                   (1000, 96, 72), (2048, 512, 1024), (1, 4096, 12288)])
+def test_gemm_tc(M, N, K):
+    """The tensor-core product in both of its forms (weights on the wide side for few rows, rows
+    on the wide side for many), with sizes that are no multiple of any tile, K that is split and
+    K that is not, every output kind."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16); w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    scale = float(want.abs().max())
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    xd, wd = x.to(DEV), w.to(DEV)
+    assert ops.gemm_tc_accepts(xd, wd, torch.empty(M, N, device=DEV))
+    y32 = torch.full((M, N), 7.0, device=DEV)
+    ops.gemm_tc(xd, wd, y32, error_flag=flag)
+    err = float((y32.double().cpu() - want).abs().max())
+    assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)), f"float32 out: |diff| {err:.3e} of {scale:.3e}"
+    y16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(xd, wd, y16, error_flag=flag)
+    close(y16, want, torch.bfloat16)
+    base = torch.randn(M, N, generator=g)
+    acc = base.to(DEV).clone()
+    ops.gemm_tc(xd, wd, acc, accumulate=True, error_flag=flag)
+    err = float((acc.double().cpu() - (base.double() + want)).abs().max())
+    assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)) + 1e-6
+    assert flag.tolist() == [0, 0, 0, 0]
+    plan = ops.gemm_tc_plan(M, N, K, DEV)
+    assert plan["swapped"] == (M <= 128)
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch():
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(64, 4096, generator=g).to(torch.bfloat16).to(DEV); w = torch.randn(512, 4096, generator=g).to(torch.bfloat16).to(DEV)
+    full = torch.empty(64, 512, device=DEV); ops.gemm_tc(x, w, full)
+    for rows in (1, 7, 16, 33):
+        part = torch.empty(rows, 512, device=DEV); ops.gemm_tc(x[20:20 + rows].contiguous(), w, part)
+        assert torch.equal(part, full[20:20 + rows]), f"{rows} rows alone differ from the same rows in a batch of 64"
+
+
+def test_gemm_tc_refusals():
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV); w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    assert not ops.gemm_tc_accepts(x, w, torch.empty(4, 8, device=DEV))          # K = 20 is no multiple of 8
+    with pytest.raises(cb.CitlaliError, match="multiple of 8"):
+        ops.gemm_tc(x, w, torch.empty(4, 8, device=DEV))
+    assert not ops.gemm_tc_accepts(x.float(), w, torch.empty(4, 8, device=DEV))
