@@ -1,0 +1,279 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Qwen3-8B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens a second at batch 8 with every sequence
+near the context length of the benchmark configuration (device time, CUDA events around K
+replayed decode steps); ``e2e`` is the same through ``InferenceSession.decode`` with the
+step's tokens coming from pinned host memory and the sampled tokens read back every step.
+``prefill`` times one 2,048-token prompt; ``roofline`` relates the decode step to the bytes it
+must read; ``points`` give decode at batch 1 and 64.  Several GPUs are not supported.
+"""
+import argparse
+import dataclasses
+import json
+import os
+import random
+import re
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}     # an earlier measurement on this pool
+QWEN3_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, context=4096, prefill_tokens=2048)
+
+
+def benchmark_shape():
+    """The sizes of BASELINE.json's configs[2] (a sentence), read from it where it can be parsed."""
+    shape = dict(QWEN3_8B)
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            text = json.load(f)["configs"][2]
+        def num(pattern, cast=int):
+            m = re.search(pattern, text)
+            return cast(m.group(1).replace(",", "")) if m else None
+        for key, pattern in (("num_hidden_layers", r"(\d+) layers"), ("hidden_size", r"hidden (\d+)"),
+                             ("num_attention_heads", r"(\d+) q heads"), ("num_key_value_heads", r"(\d+) kv heads"),
+                             ("head_dim", r"head_dim (\d+)"), ("intermediate_size", r"intermediate (\d+)"),
+                             ("vocab_size", r"vocab (\d+)"), ("context", r"Context (\d+)"),
+                             ("prefill_tokens", r"prefill ([\d,]+)-token")):
+            v = num(pattern)
+            if v:
+                shape[key] = v
+        shape["tie_word_embeddings"] = "untied" not in text
+    except Exception:
+        pass
+    return shape
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi in the background while something is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 6:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for name, v in zip(names, f[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a CMake/C++ project with no Python package to install (no setup.py or "
+                          "pyproject.toml), cannot batch, and has no safetensors, bfloat16 or prefill path"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported (this library runs on a single device)")
+        return 2
+
+    import torch
+    import citlali_b200 as cb
+    from citlali_b200 import ops
+
+    shape = benchmark_shape()
+    layers_full = shape["num_hidden_layers"]
+    layers = args.layers or layers_full
+    context, prefill_tokens = shape["context"], shape["prefill_tokens"]
+    K, W = args.steps, max(args.warmup, 3)
+    cfg = cb.config_from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=shape["hidden_size"],
+        num_attention_heads=shape["num_attention_heads"], num_key_value_heads=shape["num_key_value_heads"],
+        head_dim=shape["head_dim"], intermediate_size=shape["intermediate_size"], vocab_size=shape["vocab_size"],
+        rope_theta=shape["rope_theta"], rms_norm_eps=shape["rms_norm_eps"],
+        tie_word_embeddings=shape["tie_word_embeddings"], max_position_embeddings=max(context, 40960)))
+    pk = peaks()
+    max_batch = 64 if not args.skip_points else args.batch
+    t_load = time.time()
+    session = cb.InferenceSession().load_random(cfg, seed=1, max_context=context, dtype="bfloat16", device="cuda:0",
+                                                max_batch=max_batch)
+    for g in session.cache.kv_groups:            # keys and values of the assumed context: synthetic
+        g.keys.normal_(0.0, 0.5); g.values.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    print(f"[bench] model of {layers} layers ready in {time.time() - t_load:.0f} s", file=sys.stderr, flush=True)
+    vocab = cfg.vocab_size
+    rng = random.Random(0)
+    clocks = ClockSampler()
+    clocks.start()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    weight_bytes = session.model.weight_bytes_read_per_step()
+    kv_bytes_per_token = sum(2 * g.requirement.num_kv_heads * g.requirement.head_dim * 2 * len(g.steps)
+                             for g in session.cache.kv_groups)
+
+    # ---- prefill: one prompt of 2,048 tokens ----------------------------------------------
+    prompt = [rng.randrange(vocab) for _ in range(prefill_tokens)]
+    times = []
+    for i in range(3 + 3):
+        slot = session.acquire()
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        logits = session.step([cb.StepEntry(slot, prompt, [prefill_tokens - 1])])
+        session.sampler.sample_device(logits, 0.0, [])
+        b.record()
+        torch.cuda.synchronize()
+        session.release(slot)
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    prefill_ms = statistics.median(times)
+    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I
+    T = prefill_tokens
+    prefill_flops = 2.0 * T * layer_params * layers + 2.0 * H * vocab + layers * 4.0 * (T * (T + 1) / 2) * d * nq
+    prefill = {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
+               "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "tflops": prefill_flops / (prefill_ms / 1e3) / 1e12}
+    print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+
+    # ---- decode -----------------------------------------------------------------------------
+    def decode_run(batch, steps, warm, end_to_end):
+        """Tokens a second, ms a step, kernels launched and the mean cached length, over `steps`
+        decode steps that end at the context length."""
+        start_len = context - (warm + steps) - 1
+        slots = [session.acquire() for _ in range(batch)]
+        for s in slots:
+            session.assume_cached(s, start_len)
+        tokens = [rng.randrange(vocab) for _ in range(batch)]
+        launches = 0
+        if end_to_end:
+            for _ in range(warm):
+                tokens = session.decode(slots, tokens, 0.0, [])
+            torch.cuda.synchronize()
+            before = ops.launch_count()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                tokens = session.decode(slots, tokens, 0.0, [])
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - t0
+            launches = steps * session.runner.kernels_per_replay[(batch, True)] + ops.launch_count() - before
+        else:
+            runner = session.runner
+            runner.launch(slots, tokens, 0.0, [])
+            for _ in range(warm - 1):
+                runner.feed_back(batch)
+                runner.launch(slots, None, 0.0, [])
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(steps):
+                runner.feed_back(batch)
+                launches += runner.launch(slots, None, 0.0, [])
+            b.record()
+            torch.cuda.synchronize()
+            seconds = a.elapsed_time(b) / 1e3
+        session.check_device_errors()
+        mean_len = start_len + warm + (steps - 1) / 2.0 + 1
+        for s in slots:
+            session.release(s)
+        return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3, "launches": launches, "mean_len": mean_len}
+
+    main_run = decode_run(args.batch, K, W, False)
+    print(f"[bench] decode b{args.batch} {main_run}", file=sys.stderr, flush=True)
+    e2e_run = decode_run(args.batch, K, W, True)
+    print(f"[bench] e2e b{args.batch} {e2e_run}", file=sys.stderr, flush=True)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = decode_run(b, min(K, 32), W, False)
+            points[f"decode_b{b}"] = r["tok_s"]
+            print(f"[bench] decode b{b} {r}", file=sys.stderr, flush=True)
+    clock_record = clocks.stop()
+
+    step_bytes = weight_bytes + args.batch * main_run["mean_len"] * kv_bytes_per_token
+    achieved = step_bytes / (main_run["ms"] / 1e3) / 1e9
+    runner = session.runner
+    h2d = int(runner._offsets[6] * 4)
+    line = {
+        "metric": "decode tok/s @ batch 8 (Qwen3-8B shape, random bf16 weights)",
+        "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": main_run["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids, cache of the assumed context filled with random keys and values",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": layers_full, "hidden": H,
+                   "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": vocab,
+                   "global_batch": args.batch, "seq_len": context, "prefill_tokens": prefill_tokens,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2: every step reads all weights",
+                   "peaks": pk["source"]},
+        "e2e": {"value": e2e_run["tok_s"], "unit": "tok/s", "ms_per_step": e2e_run["ms"],
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": main_run["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+        "points": points,
+        "clocks": clock_record,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -50,6 +50,17 @@ int citlali_attention_rows(const void* q, int q_stride, int dtype,
                            int page_size, int window, int max_keys, float scale,
                            cudaStream_t stream);
 
+// Attention of single new tokens (bfloat16) split over the context; positions are read on the
+// device, `max_positions` bounds them and fixes the grid.  `partial` is float scratch of
+// citlali_attention_decode_scratch_floats(...) elements.
+size_t citlali_attention_decode_scratch_floats(int rows, int nq, int head_dim, int page_size, int max_positions);
+int citlali_attention_decode(const void* q, int q_stride, const void* k_pool, const void* v_pool,
+                             const int32_t* page_table, int page_table_stride,
+                             const int32_t* row_slot, const int32_t* row_pos,
+                             void* out, int out_stride, float* partial, size_t partial_floats,
+                             int rows, int nq, int nkv, int head_dim, int page_size, int window,
+                             int max_positions, float scale, cudaStream_t stream);
+
 // tokens[r] = argmax of logits[r, :] over finite values, lowest index on ties.
 int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int vocab, cudaStream_t stream);
 

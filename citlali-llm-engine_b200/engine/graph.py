@@ -1,0 +1,149 @@
+"""Decoding through CUDA graphs.
+
+One decode step launches a few hundred small kernels; at batch 1 their launch cost on the
+host would exceed the time the GPU needs.  The step for a given number of sequences is
+therefore captured once and replayed.  Everything that changes from step to step lives in
+device buffers of fixed address: the tokens, each row's slot and position, the sampling
+parameters, the page tables.  The host fills a pinned mirror, issues one copy, and replays.
+
+A model can be replayed only if none of its parts looks at the host-side lists of a step
+(slots, lengths): parts say so with ``graph_safe = True``; for other models the session
+keeps stepping without graphs.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..errors import require
+from ..parts.base import StepBatch
+
+
+def model_is_graph_safe(model) -> bool:
+    if model.ctx.dtype != torch.bfloat16:
+        return False          # the 32-bit attention kernel sizes its shared memory from the lengths
+    for block in model.layers:
+        for part in block.parts():
+            if not getattr(part, "graph_safe", False):
+                return False
+    return True
+
+
+class DecodeGraphRunner:
+    def __init__(self, model, cache, max_batch: int):
+        self.model = model
+        self.cache = cache
+        self.max_batch = max_batch
+        dev = model.ctx.device
+        B = max_batch
+        # int32 layout: tokens | row_slot | row_pos | seq_start | seq_slot | seq_past | want_rows
+        self._sizes = [B, B, B, B + 1, B, B, B]
+        self._offsets = [0]
+        for s in self._sizes:
+            self._offsets.append(self._offsets[-1] + (s + 3) // 4 * 4)
+        self.ints_host = torch.zeros(self._offsets[-1], dtype=torch.int32, pin_memory=True)
+        self.ints = torch.zeros(self._offsets[-1], dtype=torch.int32, device=dev)
+        self.floats_host = torch.zeros((2, B), dtype=torch.float32, pin_memory=True)   # temperature, uniform
+        self.floats = torch.zeros((2, B), dtype=torch.float32, device=dev)
+        self.out_tokens = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.out_host = torch.zeros(B, dtype=torch.int32, pin_memory=True)
+        self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self.logits: Dict[Tuple[int, bool], torch.Tensor] = {}
+        self.kernels_per_replay: Dict[Tuple[int, bool], int] = {}
+        self._pool = None
+        # constant parts of the mirror: one row per sequence
+        seq_start = self._piece(self.ints_host, 3, B + 1)
+        seq_start.copy_(torch.arange(B + 1, dtype=torch.int32))
+        self._piece(self.ints_host, 6, B).copy_(torch.arange(B, dtype=torch.int32))
+        self.ints.copy_(self.ints_host)
+
+    def _piece(self, buf, i, n):
+        return buf[self._offsets[i]:self._offsets[i] + n]
+
+    def _batch(self, n: int) -> StepBatch:
+        d = self.ints
+        return StepBatch(self._piece(d, 0, n), self._piece(d, 1, n), self._piece(d, 2, n), self._piece(d, 3, n + 1),
+                         self._piece(d, 4, n), self._piece(d, 5, n), self._piece(d, 6, n),
+                         slots=[0] * n, past=[0] * n, n_new=[1] * n)
+
+    def _body(self, n: int, greedy: bool):
+        logits = self.model.forward(self._batch(n), self.cache)
+        if greedy:
+            ops.argmax_rows(logits, self.out_tokens[:n])
+        else:
+            ops.sample_rows(logits, self.floats[0], self.floats[1], self.out_tokens[:n])
+        return logits
+
+    def _graph(self, n: int, greedy: bool) -> torch.cuda.CUDAGraph:
+        key = (n, greedy)
+        g = self.graphs.get(key)
+        if g is not None:
+            return g
+        # run once outside capture: compiles nothing, but sizes scratch buffers and sets kernel attributes
+        side = torch.cuda.Stream(device=self.model.ctx.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._body(n, greedy)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(g, pool=self._pool):
+            self.logits[key] = self._body(n, greedy)
+        self.kernels_per_replay[key] = ops.launch_count() - before
+        if self._pool is None:
+            self._pool = g.pool()
+        self.graphs[key] = g
+        return g
+
+    def fill(self, slots: Sequence[int], tokens: Optional[Sequence[int]], positions: Sequence[int],
+             temperature: float, uniforms: Sequence[float]) -> None:
+        """Write the step's inputs into the pinned mirror and issue the copies.  ``tokens`` None:
+        keep the device's token buffer (fed from the last step's output on the device)."""
+        n = len(slots)
+        h = self.ints_host
+        if tokens is not None:
+            self._piece(h, 0, n).copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
+        slot_t = torch.as_tensor(list(slots), dtype=torch.int32)
+        pos_t = torch.as_tensor(list(positions), dtype=torch.int32)
+        self._piece(h, 1, n).copy_(slot_t)
+        self._piece(h, 2, n).copy_(pos_t)
+        self._piece(h, 4, n).copy_(slot_t)
+        self._piece(h, 5, n).copy_(pos_t)
+        lo = 0 if tokens is not None else self._offsets[1]
+        hi = self._offsets[6]
+        self.ints[lo:hi].copy_(h[lo:hi], non_blocking=True)
+        if temperature > 0.0:
+            self.floats_host[0, :n] = float(temperature)
+            self.floats_host[1, :n] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+            self.floats.copy_(self.floats_host, non_blocking=True)
+
+    def launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]], temperature: float,
+               uniforms: Sequence[float]) -> int:
+        """Reserve cache room, copy the inputs, replay the graph, advance the lengths.  Returns the
+        number of kernels the replay launched.  Nothing is synchronised."""
+        n = len(slots)
+        require(0 < n <= self.max_batch, f"{n} sequences exceed the runner's {self.max_batch}")
+        positions = [self.cache.length(s) for s in slots]
+        greedy = temperature <= 0.0
+        for s, p in zip(slots, positions):
+            self.cache.reserve(s, p + 1)
+        self.fill(slots, tokens, positions, temperature, uniforms)
+        # the inputs are in place before a first capture: its trial run is then this very step,
+        # and running a step twice writes the same keys and values twice
+        g = self._graph(n, greedy)
+        g.replay()
+        for s, p in zip(slots, positions):
+            self.cache.commit(s, p + 1)
+        return self.kernels_per_replay[(n, greedy)]
+
+    def feed_back(self, n: int) -> None:
+        """Make the tokens just sampled the next step's input, on the device."""
+        self._piece(self.ints, 0, n).copy_(self.out_tokens[:n], non_blocking=True)
+
+    def read_tokens(self, n: int) -> List[int]:
+        self.out_host[:n].copy_(self.out_tokens[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.out_host[:n].tolist()

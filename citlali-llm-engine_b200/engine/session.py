@@ -20,6 +20,7 @@ from ..parts.base import BuildContext
 from ..sampling.sampler import Sampler
 from ..weights.loader import WeightHandle, WeightLoader
 from ..weights.random_init import random_weights
+from .graph import DecodeGraphRunner, model_is_graph_safe
 from .generate import GenerationOptions, GenerationResult, run_generation
 from .model import DecoderModel
 from .step import StepEntry, pack_step
@@ -50,6 +51,8 @@ class InferenceSession:
         self.sampler: Optional[Sampler] = None
         self.max_context = 0
         self.stats: Dict[str, float] = {}
+        self.runner = None
+        self.use_graphs = True     # set False before loading to step without CUDA graphs
 
     # ---- loading ---------------------------------------------------------------------
     def load_model(self, model_path: str, max_context: int = 2048, dtype="bfloat16", device="cuda:0",
@@ -106,6 +109,8 @@ class InferenceSession:
                                    model.ctx.dtype, model.ctx.device, page_size=page)
         self.sampler = Sampler(model.ctx.device, max_rows=max_batch)
         self.max_batch = max_batch
+        self.runner = DecodeGraphRunner(model, self.cache, max_batch) if (
+            self.use_graphs and model_is_graph_safe(model)) else None
         return self
 
     # ---- slots and steps -----------------------------------------------------------------
@@ -140,6 +145,14 @@ class InferenceSession:
             self.cache.commit(e.slot, p + len(e.tokens))
         return logits
 
+    def assume_cached(self, slot: int, tokens: int) -> None:
+        """Declare that ``slot`` holds ``tokens`` tokens without computing them: room is reserved
+        and the length is set, the keys and values are whatever the cache's memory holds.  For
+        measurements at a given context length only."""
+        require(tokens <= self.max_context, f"{tokens} tokens exceed max_context {self.max_context}")
+        self.cache.reserve(slot, tokens)
+        self.cache.commit(slot, tokens)
+
     def check_device_errors(self) -> None:
         """Read the word kernels raise when they meet a fault they can detect (a token id outside
         the embedding table, a wait that ran out).  Synchronises."""
@@ -161,8 +174,18 @@ class InferenceSession:
 
     def decode(self, slots, tokens, temperature, uniforms) -> List[int]:
         t0 = time.perf_counter()
-        logits = self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
-        out = self.sampler.sample(logits, temperature, uniforms)
+        if self.runner is not None and len(slots) <= self.runner.max_batch:
+            vocab = self.model.spec.vocab_size
+            for s, t in zip(slots, tokens):
+                require(self.cache.slots.is_held(s), f"slot {s} was not acquired")
+                require(0 <= int(t) < vocab, f"token id {t} out of vocab range [0, {vocab})")
+                require(self.cache.length(s) + 1 <= self.max_context,
+                        f"slot {s}: one more token exceeds max_context {self.max_context}")
+            self.runner.launch(slots, tokens, temperature, uniforms)
+            out = self.runner.read_tokens(len(slots))
+        else:
+            logits = self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
+            out = self.sampler.sample(logits, temperature, uniforms)
         self.stats["decode_s"] = self.stats.get("decode_s", 0.0) + time.perf_counter() - t0
         self.stats["decode_tokens"] = self.stats.get("decode_tokens", 0) + len(slots)
         return out

@@ -46,8 +46,20 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_launches = 0
+_KERNELS_PER_CALL = {"gemm_tc": 1, "attention_decode": 2}
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far through this module (a split-K product counts
+    its reduction, split-context attention its merge)."""
+    return _launches
+
+
 def _check(code: int, what: str):
+    global _launches
     if code == 0:
+        _launches += _KERNELS_PER_CALL.get(what, 1)
         return
     if code < 0:
         raise CitlaliError(f"{what} refused: {lib().citlali_last_error().decode()}")
@@ -160,10 +172,34 @@ def sample_rows(logits, temperature, uniform, tokens):
 
 def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, scale):
     """Attention of every row of the step over its slot's cache.  ``q`` holds the rotated
-    queries with ``q_stride`` elements between rows."""
+    queries with ``q_stride`` elements between rows.  bfloat16 steps in which every sequence
+    brings one token run the split-context kernel, whose launch does not depend on the
+    sequences' lengths; everything else runs the generic kernel."""
+    if q.dtype == torch.bfloat16 and batch.is_decode and head_dim % 8 == 0 and head_dim <= 256:
+        attention_decode(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table, batch.row_slot,
+                         batch.row_pos, out, nq, nkv, head_dim, cache_view.page_size, window,
+                         cache_view.page_table.shape[1] * cache_view.page_size, scale)
+        return
     attention_rows(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table,
                    batch.row_slot, batch.row_pos, out, nq, nkv, head_dim, cache_view.page_size,
                    window, batch.max_keys, scale)
+
+
+def attention_decode(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos, out, nq, nkv, head_dim,
+                     page_size, window, max_positions, scale):
+    _need_cuda(k_pool, v_pool, page_table, row_slot, row_pos, out)
+    require(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+            "attention_decode: bfloat16 only")
+    rows = out.shape[0]
+    l = lib()
+    l.citlali_attention_decode_scratch_floats.restype = ctypes.c_size_t
+    need = l.citlali_attention_decode_scratch_floats(_i(rows), _i(nq), _i(head_dim), _i(page_size), _i(max_positions))
+    ws = _scratch(q.device, "attention_decode", need * 4)
+    _check(l.citlali_attention_decode(
+        _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
+        _ptr(row_slot), _ptr(row_pos), _ptr(out), _i(out.shape[1]), _ptr(ws), ctypes.c_size_t(ws.numel() // 4),
+        _i(rows), _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(max_positions), _f(scale),
+        _stream()), "attention_decode")
 
 
 _sm_count = {}
@@ -186,17 +222,21 @@ def gemm_tc_plan(M: int, N: int, K: int, device) -> dict:
     return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value, "workspace_bytes": need.value}
 
 
-def _gemm_workspace(device, nbytes: int) -> torch.Tensor:
-    """One scratch buffer per device for split-K partials; it only grows.  Kernels on one stream
-    use it one after another."""
-    key = torch.device(device).index or 0
+def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
+    """One scratch buffer per device and purpose (split-K partials, split-context attention
+    partials); it only grows.  Kernels on one stream use it one after another."""
+    key = (torch.device(device).index or 0, purpose)
     ws = _workspace.get(key)
     if ws is None or ws.numel() < nbytes:
         require(not torch.cuda.is_current_stream_capturing(),
-                "the split-K scratch buffer would have to grow during graph capture; run the step once before capturing")
+                f"the {purpose} scratch buffer would have to grow during graph capture; run the step once before capturing")
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
     return ws
+
+
+def _gemm_workspace(device, nbytes: int) -> torch.Tensor:
+    return _scratch(device, "gemm split-K", nbytes)
 
 
 def gemm_tc_accepts(x, w, y) -> bool:
@@ -218,3 +258,6 @@ def gemm_tc(x, w, y, accumulate=False, error_flag=None):
     _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K),
                                  _i(1 if accumulate else 0), _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
                                  _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")
+    if need:
+        global _launches
+        _launches += 1          # the split-K reduction

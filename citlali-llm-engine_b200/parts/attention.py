@@ -27,6 +27,8 @@ from .linear import DenseLinear
 
 
 class GQAttention:
+    graph_safe = True      # reads slots and positions from device memory only
+
     def __init__(self, params, prefix: str):
         self.hidden = int(params["hidden_size"])
         self.nq = int(params["num_heads"])

@@ -18,6 +18,8 @@ _RUN = 16
 
 
 class GatedSiluFeedForward:
+    graph_safe = True
+
     def __init__(self, params, prefix: str):
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])

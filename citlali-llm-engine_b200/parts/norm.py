@@ -13,6 +13,8 @@ from .base import register_part
 
 
 class RMSNorm:
+    graph_safe = True
+
     def __init__(self, params, prefix: str):
         self.size = int(params["size"])
         self.eps = float(params["eps"])

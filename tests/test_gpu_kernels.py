@@ -331,3 +331,34 @@ def test_gemm_tc_refusals():
     with pytest.raises(cb.CitlaliError, match="multiple of 8"):
         ops.gemm_tc(x, w, torch.empty(4, 8, device=DEV))
     assert not ops.gemm_tc_accepts(x.float(), w, torch.empty(4, 8, device=DEV))
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 64, 0), (6, 3, 48, 64, 0), (5, 5, 80, 8, 0), (32, 8, 128, 64, 0),
+                                                  (12, 1, 64, 16, 0), (8, 2, 256, 64, 0), (6, 2, 112, 64, 300), (4, 2, 32, 8, 5)])
+def test_attention_decode_split_over_the_context(nq, nkv, d, page, window):
+    """Single new tokens at positions from 0 to 1100 (one to five chunks of four pages), several
+    sequences at once, against the plain implementation; one sequence has a far key that wins."""
+    g = torch.Generator().manual_seed(nq * d + page)
+    dtype = torch.bfloat16
+    lengths = [1, 2, 65, 256, 257, 700, 1101] if page == 64 else [1, 9, 33, 100]
+    k = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lengths]
+    v = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lengths]
+    q = [(torch.randn(1, nq, d, generator=g) * 2).to(dtype).double() for n in lengths]
+    if lengths[-1] > 600 and window == 0:
+        q[-1][0, :, 3] = 20.0; k[-1][7, :, 3] = 20.0          # key 7 of 1101 takes nearly all the weight
+    kp, vp, table = make_paged(k, v, lengths, page, dtype, seed=3)
+    B = len(lengths)
+    qrow = torch.cat([x.reshape(1, nq * d) for x in q]).to(dtype).to(DEV)
+    out = torch.empty(B, nq * d, dtype=dtype, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    ops.attention_decode(qrow, nq * d, kp.to(DEV), vp.to(DEV), table.to(DEV), slots, pos, out, nq, nkv, d, page, window,
+                         table.shape[1] * page, 1.0 / math.sqrt(d))
+    for b, n in enumerate(lengths):
+        qfull = torch.cat([torch.zeros(n - 1, nq, d, dtype=torch.float64), q[b]])
+        want = plain.causal_attention(qfull, k[b], v[b], nq, nkv, window=window or None)[-1]
+        got = out[b].view(nq, d)
+        err = float((got.double().cpu() - want).abs().max())
+        assert err <= 2 ** -8 * float(want.abs().max()), f"sequence of {n}: |diff| {err:.3e}"
+    if lengths[-1] > 600 and window == 0:
+        assert (out[-1].view(nq, d)[0].double().cpu() - v[-1][7, 0]).abs().max() < 0.1
