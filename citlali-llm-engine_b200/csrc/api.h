@@ -61,6 +61,16 @@ int citlali_attention_decode(const void* q, int q_stride, const void* k_pool, co
                              int rows, int nq, int nkv, int head_dim, int page_size, int window,
                              int max_positions, float scale, cudaStream_t stream);
 
+// Causal attention of runs of new tokens (bfloat16, pages of 64) on the tensor cores.  Sequence b
+// owns rows seq_start[b] .. seq_start[b+1]-1 at positions seq_past[b] + i of slot seq_slot[b].
+int citlali_attention_prefill_supports(int head_dim, int page_size);
+int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, const void* v_pool,
+                              const int32_t* page_table, int page_table_stride,
+                              const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
+                              void* out, int out_stride, int sequences, int max_new,
+                              int nq, int nkv, int head_dim, int page_size, int window, float scale,
+                              cudaStream_t stream);
+
 // tokens[r] = argmax of logits[r, :] over finite values, lowest index on ties.
 int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int vocab, cudaStream_t stream);
 

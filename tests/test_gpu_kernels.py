@@ -362,3 +362,38 @@ def test_attention_decode_split_over_the_context(nq, nkv, d, page, window):
         assert err <= 2 ** -8 * float(want.abs().max()), f"sequence of {n}: |diff| {err:.3e}"
     if lengths[-1] > 600 and window == 0:
         assert (out[-1].view(nq, d)[0].double().cpu() - v[-1][7, 0]).abs().max() < 0.1
+
+
+@pytest.mark.parametrize("nq,nkv,d,window", [(4, 2, 16, 0), (6, 3, 48, 0), (3, 1, 80, 0), (8, 2, 128, 0), (2, 2, 256, 0),
+                                             (4, 1, 64, 0), (5, 5, 112, 100), (4, 2, 32, 7), (2, 1, 96, 64)])
+def test_attention_prefill_flash(nq, nkv, d, window):
+    """Prompts and runs of tokens that continue a sequence, of lengths around the 64-token tiles,
+    several sequences in one launch, against the plain implementation."""
+    g = torch.Generator().manual_seed(nq * d + 1)
+    dtype = torch.bfloat16
+    past, n_new = [0, 130, 5, 0, 63, 200], [37, 1, 64, 129, 66, 300]
+    k = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    v = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    qfull = [(torch.randn(p + n, nq, d, generator=g) * 1.5).to(dtype).double() for p, n in zip(past, n_new)]
+    qfull[5][450, :, 2] = 18.0; k[5][11, :, 2] = 18.0           # row 450 finds key 11 among 451
+    lengths = [p + n for p, n in zip(past, n_new)]
+    kp, vp, table = make_paged(k, v, lengths, 64, dtype, seed=5)
+    qq = torch.cat([qf[p:].reshape(-1, nq * d) for qf, p in zip(qfull, past)]).to(dtype)
+    pad = torch.randn(qq.shape[0], 8).to(dtype)
+    qrow = torch.cat([qq, pad], dim=1).contiguous().to(DEV)
+    out = torch.empty(qq.shape[0], nq * d, dtype=dtype, device=DEV)
+    starts = [0]
+    for n in n_new:
+        starts.append(starts[-1] + n)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    ops.attention_prefill(qrow, qrow.shape[1], kp.to(DEV), vp.to(DEV), table.to(DEV), i32(starts), i32(list(range(6))),
+                          i32(past), out, 6, max(n_new), nq, nkv, d, 64, window, 1.0 / math.sqrt(d))
+    for b in range(6):
+        want = plain.causal_attention(qfull[b], k[b], v[b], nq, nkv, window=window or None)[past[b]:]
+        got = out[starts[b]:starts[b + 1]].view(-1, nq, d)
+        err = float((got.double().cpu() - want).abs().max())
+        # P is rounded to bfloat16 before it multiplies V: 2^-9 relative per term on top of the output's rounding
+        assert err <= 2 ** -7 * float(want.abs().max()), f"sequence {b}: |diff| {err:.3e} of {float(want.abs().max()):.3e}"
+    if window == 0:
+        assert (out[starts[5] + 250].view(nq, d)[0].double().cpu() - v[5][11, 0]).abs().max() < 0.1
+    assert not ops.lib().citlali_attention_prefill_supports(40, 64) and not ops.lib().citlali_attention_prefill_supports(128, 16)
