@@ -13,6 +13,7 @@
 // sum of values; query head j reads key/value head j / (heads / kv_heads).
 #include "api.h"
 #include "common.cuh"
+#include "mma_common.cuh"
 
 namespace citlali {
 
@@ -154,7 +155,7 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
             for (int e = 0; e < EPL; ++e) out[e] = fmaf(slot[2 + e0 + e], f, out[e]);
         }
         float* dst = partial + (((size_t)row * nq + head0 + h) * max_chunks + chunk) * (d + 2);
-        if (lane == 0) { dst[0] = M; dst[1] = L; }
+        if (lane == 0) { dst[0] = M * 1.4426950408889634f; dst[1] = L; }   // maxima are stored in log2 units
         if (lane_on) {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) dst[2 + e0 + e] = out[e];
@@ -162,26 +163,227 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
     }
 }
 
-// out[row, head, :] = sum_c exp(m_c - M) acc_c / sum_c exp(m_c - M) l_c over the row's visible
-// chunks, in chunk order.
-__global__ void attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunks,
-                                                const int32_t* __restrict__ row_pos, __nv_bfloat16* __restrict__ out,
-                                                int out_stride, int nq, int d, int chunk_keys, int window) {
+// out[row, head, :] = sum_c 2^(m_c - M) acc_c / sum_c 2^(m_c - M) l_c over the row's visible
+// chunks, in chunk order (m_c in log2 units).
+__global__ void __launch_bounds__(128)
+attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunks,
+                                const int32_t* __restrict__ row_pos, __nv_bfloat16* __restrict__ out,
+                                int out_stride, int nq, int d, int chunk_keys, int window) {
+    extern __shared__ float weight[];                           // [chunks]: 2^(m_c - M), then the total in [chunks]
     const int head = blockIdx.x, row = blockIdx.y;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int c0 = lo / chunk_keys, c1 = pos / chunk_keys;
-    const float* base = partial + ((size_t)row * nq + head) * max_chunks * (d + 2);
-    float M = -INFINITY;
-    for (int c = c0; c <= c1; ++c) M = fmaxf(M, base[(size_t)c * (d + 2)]);
-    float L = 0.0f;
-    for (int c = c0; c <= c1; ++c) L += base[(size_t)c * (d + 2) + 1] * __expf(base[(size_t)c * (d + 2)] - M);
-    const float inv = 1.0f / L;
+    const int c0 = lo / chunk_keys, c1 = pos / chunk_keys, n = c1 - c0 + 1;
+    const float* base = partial + (((size_t)row * nq + head) * max_chunks + c0) * (d + 2);
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int c = threadIdx.x; c < n; c += 32) M = fmaxf(M, base[(size_t)c * (d + 2)]);
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int c = threadIdx.x; c < n; c += 32) {
+            const float w = exp2f(base[(size_t)c * (d + 2)] - M);
+            weight[c] = w;
+            L += base[(size_t)c * (d + 2) + 1] * w;
+        }
+        L = warp_sum(L);
+        if (threadIdx.x == 0) weight[n] = 1.0f / L;
+    }
+    __syncthreads();
+    const float inv = weight[n];
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float a = 0.0f;
-        for (int c = c0; c <= c1; ++c) a = fmaf(base[(size_t)c * (d + 2) + 2 + i], __expf(base[(size_t)c * (d + 2)] - M), a);
+        for (int c = 0; c < n; ++c) a = fmaf(base[(size_t)c * (d + 2) + 2 + i], weight[c], a);
         out[(size_t)row * out_stride + (size_t)head * d + i] = __float2bfloat16_rn(a * inv);
     }
+}
+
+// The same work on the tensor cores, for pages of 64 keys.  The rows of the MMA are the query
+// heads that share the key/value head (padded to 16), so a key or value read from the cache
+// serves all of them.  The block walks its chunk one page at a time (cp.async, double-buffered);
+// each warp takes 16 keys of the page: S = Q K^T (mma.sync m16n8k16), online softmax in float,
+// O += P V.  At the end the four warps' (m, l, O) are merged through shared memory and written
+// as the chunk's partial, maxima in log2 units.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
+                           const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                           const int32_t* __restrict__ page_table, int page_table_stride,
+                           const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                           float* __restrict__ partial, int max_chunks, int nq, int nkv, int window, float scale_log2) {
+    using namespace fa;
+    constexpr int kPage = 64;
+    constexpr int kRowBytes = D * 2 + 16;
+    constexpr int kTileBytes = kPage * kRowBytes;
+    constexpr int kChunksPerRow = D / 8;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);          // 16 rows
+    const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + 2 * kTileBytes;
+
+    const int chunk = blockIdx.x;
+    const int group = nq / nkv;
+    const int row_tiles = (group + 15) / 16;
+    const int g = blockIdx.y / row_tiles;
+    const int head0 = g * group + (blockIdx.y % row_tiles) * 16;
+    const int heads_here = min(16, g * group + group - head0);
+    const int row = blockIdx.z;
+    const int pos = row_pos[row];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int chunk_keys = kChunkPages * kPage;
+    if (chunk * chunk_keys > pos || chunk * chunk_keys + chunk_keys <= lo) return;
+    const int tile_lo = max(chunk * kChunkPages, lo / kPage), tile_hi = min(chunk * kChunkPages + kChunkPages - 1, pos / kPage);
+    const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+
+    for (int c = tid; c < 16 * kChunksPerRow; c += 128) {
+        const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
+        if (r < heads_here) cp_async16(s_q + r * kRowBytes + ch * 16, q + (size_t)row * q_stride + (size_t)(head0 + r) * D + ch * 8);
+        else *reinterpret_cast<uint4*>(smem + r * kRowBytes + ch * 16) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+    auto load_tile = [&](int tile, int buf) {
+        const size_t base = ((size_t)pages[tile] * nkv + g) * kPage * D;
+        for (int c = tid; c < kPage * kChunksPerRow; c += 128) {
+            const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
+            const size_t src = base + (size_t)r * D + ch * 8;
+            cp_async16(s_k + buf * kTileBytes + r * kRowBytes + ch * 16, k_pool + src);
+            cp_async16(s_v + buf * kTileBytes + r * kRowBytes + ch * 16, v_pool + src);
+        }
+    };
+    load_tile(tile_lo, 0);
+    cp_async_commit();
+
+    uint32_t qf[D / 16][4];
+    cp_async_wait<1>();
+    __syncthreads();
+    {
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int cbyte = (lane >> 4) * 16;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+            ldmatrix_x4(s_q + r * kRowBytes + ks * 32 + cbyte, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+    for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+        const int buf = (tile - tile_lo) & 1;
+        if (tile + 1 <= tile_hi) load_tile(tile + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kb = s_k + buf * kTileBytes + warp * 16 * kRowBytes, vb = s_v + buf * kTileBytes + warp * 16 * kRowBytes;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int r = (lane & 7) + (lane >> 4) * 8;
+            const int cbyte = ((lane >> 3) & 1) * 16;
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(kb + r * kRowBytes + ks * 32 + cbyte, b0, b1, b2, b3);
+            mma_16816(s[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+            mma_16816(s[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+        }
+        const int key_base = tile * kPage + warp * 16 + (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int key = key_base + i * 8;
+            if (key > pos || key < lo) { s[i][0] = -INFINITY; s[i][2] = -INFINITY; }
+            if (key + 1 > pos || key + 1 < lo) { s[i][1] = -INFINITY; s[i][3] = -INFINITY; }
+        }
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ref0 = mn0 == -INFINITY ? 0.0f : mn0 * scale_log2, ref1 = mn1 == -INFINITY ? 0.0f : mn1 * scale_log2;
+        const float a0 = exp2f(m0 * scale_log2 - ref0), a1 = exp2f(m1 * scale_log2 - ref1);
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            s[i][0] = exp2f(s[i][0] * scale_log2 - ref0); s[i][1] = exp2f(s[i][1] * scale_log2 - ref0);
+            s[i][2] = exp2f(s[i][2] * scale_log2 - ref1); s[i][3] = exp2f(s[i][3] * scale_log2 - ref1);
+        }
+        l0 = l0 * a0 + s[0][0] + s[0][1] + s[1][0] + s[1][1];
+        l1 = l1 * a1 + s[0][2] + s[0][3] + s[1][2] + s[1][3];
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+        const uint32_t p0 = pack_bf16(s[0][0], s[0][1]), p1 = pack_bf16(s[0][2], s[0][3]);
+        const uint32_t p2 = pack_bf16(s[1][0], s[1][1]), p3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int np = 0; np < D / 16; ++np) {
+            const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int cbyte = np * 32 + (lane >> 4) * 16;
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(vb + r * kRowBytes + cbyte, b0, b1, b2, b3);
+            mma_16816(o[2 * np], p0, p1, p2, p3, b0, b1);
+            mma_16816(o[2 * np + 1], p0, p1, p2, p3, b2, b3);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // park every warp's (m in log2 units, l, O) over the tile buffers, then merge per head
+    float* park = reinterpret_cast<float*>(smem + 16 * kRowBytes);                // [4 warps][16 rows][D + 2]
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8, col = (lane & 3) * 2;
+        float* w0 = park + ((size_t)warp * 16 + r0) * (D + 2);
+        float* w1 = park + ((size_t)warp * 16 + r1) * (D + 2);
+        if ((lane & 3) == 0) {
+            w0[0] = m0 == -INFINITY ? -INFINITY : m0 * scale_log2; w0[1] = l0;
+            w1[0] = m1 == -INFINITY ? -INFINITY : m1 * scale_log2; w1[1] = l1;
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            w0[2 + i * 8 + col] = o[i][0]; w0[2 + i * 8 + col + 1] = o[i][1];
+            w1[2 + i * 8 + col] = o[i][2]; w1[2 + i * 8 + col + 1] = o[i][3];
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < heads_here * (D + 2); e += 128) {
+        const int h = e / (D + 2), i = e % (D + 2);
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, park[((size_t)w * 16 + h) * (D + 2)]);
+        float v;
+        if (i == 0) {
+            v = M;
+        } else {
+            v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = park[((size_t)w * 16 + h) * (D + 2)];
+                const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
+                v = fmaf(park[((size_t)w * 16 + h) * (D + 2) + i], f, v);
+            }
+        }
+        partial[(((size_t)row * nq + head0 + h) * max_chunks + chunk) * (D + 2) + i] = v;
+    }
+}
+
+template <int D>
+static int launch_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                     int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, float* partial,
+                     int max_chunks, int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
+    constexpr int tiles = (16 + 4 * 64) * (D * 2 + 16);
+    constexpr int park = 16 * (D * 2 + 16) + 4 * 16 * (D + 2) * 4;
+    constexpr int smem = tiles > park ? tiles : park;
+    auto kernel = attention_decode_tc_kernel<D>;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int group = nq / nkv;
+    dim3 grid(max_chunks, nkv * ((group + 15) / 16), rows);
+    kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
+                                        (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
+                                        partial, max_chunks, nq, nkv, window, scale * 1.4426950408889634f);
+    return CITLALI_LAUNCH_CHECK();
 }
 
 template <int EPL, int GT>
@@ -257,23 +459,36 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         return kTooLarge;
     }
     const int group = nq / nkv;
-    const int gt = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
-    int rc;
-    // elements per lane: the smallest of 1, 2, 4, 8 that covers the head with 32 lanes and divides it
-    int epl = head_dim <= 32 ? 1 : head_dim <= 64 ? 2 : head_dim <= 128 ? 4 : 8;
-    while (head_dim % epl != 0) epl *= 2;   // cannot exceed 8 since head_dim % 8 == 0
+    int rc = -1000;
+    if (page_size == 64 && q_stride % 8 == 0 && (((uintptr_t)q) & 15u) == 0) {
+#define CITLALI_TC(DD) case DD: rc = launch_tc<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, \
+                                                    partial, max_chunks, rows, nq, nkv, window, scale, stream); break
+        switch (head_dim) {
+            CITLALI_TC(16); CITLALI_TC(32); CITLALI_TC(48); CITLALI_TC(64); CITLALI_TC(80); CITLALI_TC(96); CITLALI_TC(112);
+            CITLALI_TC(128); CITLALI_TC(256);
+            default: break;
+        }
+#undef CITLALI_TC
+    }
+    if (rc == -1000) {
+        // other head sizes and page sizes: the CUDA-core kernel
+        const int gt = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
+        // elements per lane: the smallest of 1, 2, 4, 8 that covers the head with 32 lanes and divides it
+        int epl = head_dim <= 32 ? 1 : head_dim <= 64 ? 2 : head_dim <= 128 ? 4 : 8;
+        while (head_dim % epl != 0) epl *= 2;   // cannot exceed 8 since head_dim % 8 == 0
 #define CITLALI_EPL(E) rc = pick_gt<E>(gt, q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, partial, \
                                         max_chunks, rows, nq, nkv, head_dim, page_size, window, scale, stream)
-    switch (epl) {
-        case 1: CITLALI_EPL(1); break;
-        case 2: CITLALI_EPL(2); break;
-        case 4: CITLALI_EPL(4); break;
-        default: CITLALI_EPL(8); break;
-    }
+        switch (epl) {
+            case 1: CITLALI_EPL(1); break;
+            case 2: CITLALI_EPL(2); break;
+            case 4: CITLALI_EPL(4); break;
+            default: CITLALI_EPL(8); break;
+        }
 #undef CITLALI_EPL
+    }
     if (rc) return rc;
     dim3 grid(nq, rows);
-    attention_decode_combine_kernel<<<grid, 128, 0, stream>>>(partial, max_chunks, row_pos, (__nv_bfloat16*)out, out_stride,
+    attention_decode_combine_kernel<<<grid, 128, (size_t)(max_chunks + 1) * sizeof(float), stream>>>(partial, max_chunks, row_pos, (__nv_bfloat16*)out, out_stride,
                                                               nq, head_dim, chunk_keys, window);
     return CITLALI_LAUNCH_CHECK();
 }
