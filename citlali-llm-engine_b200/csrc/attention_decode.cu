@@ -57,6 +57,8 @@ attention_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
                                 const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                                 float* __restrict__ partial, int max_chunks,
                                 int nq, int nkv, int d, int page_size, int window, float scale) {
+    dependents_may_launch();
+    wait_for_predecessor();
     const int chunk = blockIdx.x;
     const int group = nq / nkv;
     const int tiles_per_kv = (group + GT - 1) / GT;
@@ -170,6 +172,8 @@ attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunk
                                 const int32_t* __restrict__ row_pos, __nv_bfloat16* __restrict__ out,
                                 int out_stride, int nq, int d, int chunk_keys, int window) {
     extern __shared__ float weight[];                           // [chunks]: 2^(m_c - M), then the total in [chunks]
+    dependents_may_launch();
+    wait_for_predecessor();
     const int head = blockIdx.x, row = blockIdx.y;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -219,6 +223,8 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);          // 16 rows
     const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + 2 * kTileBytes;
 
+    dependents_may_launch();
+    wait_for_predecessor();
     const int chunk = blockIdx.x;
     const int group = nq / nkv;
     const int row_tiles = (group + 15) / 16;
@@ -380,7 +386,7 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
     }
     const int group = nq / nkv;
     dim3 grid(max_chunks, nkv * ((group + 15) / 16), rows);
-    kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
+    launch_kernel(kernel, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                         (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
                                         partial, max_chunks, nq, nkv, window, scale * 1.4426950408889634f);
     return CITLALI_LAUNCH_CHECK();
@@ -395,7 +401,7 @@ static int launch_partial(const void* q, int q_stride, const void* k_pool, const
     const int tiles_per_kv = (group + GT - 1) / GT;
     dim3 grid(max_chunks, nkv * tiles_per_kv, rows);
     const size_t smem = (size_t)kDecodeWarps * GT * (2 + 32 * EPL) * sizeof(float);
-    attention_decode_partial_kernel<EPL, GT><<<grid, kDecodeWarps * 32, smem, stream>>>(
+    launch_kernel(attention_decode_partial_kernel<EPL, GT>, grid, kDecodeWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
         page_table_stride, row_slot, row_pos, partial, max_chunks, nq, nkv, d, page_size, window, scale);
     return CITLALI_LAUNCH_CHECK();
@@ -488,7 +494,7 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
     }
     if (rc) return rc;
     dim3 grid(nq, rows);
-    attention_decode_combine_kernel<<<grid, 128, (size_t)(max_chunks + 1) * sizeof(float), stream>>>(partial, max_chunks, row_pos, (__nv_bfloat16*)out, out_stride,
+    launch_kernel(attention_decode_combine_kernel, grid, 128, (size_t)(max_chunks + 1) * sizeof(float), stream, partial, max_chunks, row_pos, (__nv_bfloat16*)out, out_stride,
                                                               nq, head_dim, chunk_keys, window);
     return CITLALI_LAUNCH_CHECK();
 }

@@ -25,6 +25,8 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
                           const int32_t* __restrict__ page_table, int page_table_stride,
                           T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
                           int nq, int nkv, int d, float eps, int write_cache) {
+    dependents_may_launch();
+    wait_for_predecessor();
     const int row = blockIdx.x;
     const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -99,6 +101,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       int nq, int nkv, int d, int page_size, int window, float scale) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
     const int row = blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = head / (nq / nkv);
@@ -184,7 +188,7 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
     }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
-            qk_norm_rope_cache_kernel<T, TG><<<grid, 128, 0, stream>>>(
+            launch_kernel(qk_norm_rope_cache_kernel<T, TG>, grid, 128, 0, stream, 
                 (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, row_slot, row_pos, page_table,
                 page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache);
             return CITLALI_LAUNCH_CHECK();
@@ -222,7 +226,7 @@ extern "C" int citlali_attention_rows(const void* q, int q_stride, int dtype,
             if (e != cudaSuccess) return (int)e;
         }
         dim3 grid(rows, nq);
-        kernel<<<grid, 128, smem, stream>>>((const T*)q, q_stride, (const T*)k_pool, (const T*)v_pool, page_table,
+        launch_kernel(kernel, grid, 128, smem, stream, (const T*)q, q_stride, (const T*)k_pool, (const T*)v_pool, page_table,
                                              page_table_stride, row_slot, row_pos, (T*)out, out_stride, nq, nkv,
                                              head_dim, page_size, window, scale);
         return CITLALI_LAUNCH_CHECK();

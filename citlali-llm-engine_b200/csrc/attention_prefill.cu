@@ -45,6 +45,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t s_k = s_q + kTileBytes, s_v = s_k + 2 * kTileBytes;
 
+    dependents_may_launch();
+    wait_for_predecessor();
     const int seq = blockIdx.z, head = blockIdx.y;
     const int row0 = seq_start[seq], n_new = seq_start[seq + 1] - row0;
     const int q0 = (gridDim.x - 1 - blockIdx.x) * kTileQ;      // long rows first: they see the most keys
@@ -205,7 +207,7 @@ static int launch(const void* q, int q_stride, const void* k_pool, const void* v
         configured = true;
     }
     dim3 grid((max_new + kTileQ - 1) / kTileQ, nq, sequences);
-    kernel<<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
+    launch_kernel(kernel, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                                  (const __nv_bfloat16*)v_pool, page_table, page_table_stride, seq_start,
                                                  seq_slot, seq_past, (__nv_bfloat16*)out, out_stride, nq, nkv, window,
                                                  scale * 1.4426950408889634f);

@@ -26,6 +26,34 @@ enum Refusal : int {
 
 void set_last_error(const char* fmt, ...);
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// Every kernel of the library is launched so that it may start while the kernel before it on
+// the stream is still running.  The rule each kernel keeps: it says at once that its own
+// successor may be launched (dependents_may_launch), and it does not read or write any global
+// memory that other kernels write until the kernel before it has finished and its writes are
+// visible (wait_for_predecessor).  What a kernel does before that wait must only touch memory
+// that no kernel writes: weights.  Since a kernel cannot finish before its own wait has
+// returned, everything older than the predecessor has finished as well.
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool dependent_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // errors surface in cudaGetLastError
+}
+
 __device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ void stf(float* p, size_t i, float v) { p[i] = v; }

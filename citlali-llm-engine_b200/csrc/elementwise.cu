@@ -9,6 +9,9 @@
 namespace citlali {
 
 static thread_local char g_last_error[512] = "";
+static bool g_dependent_launch = true;
+
+bool dependent_launch_enabled() { return g_dependent_launch; }
 
 void set_last_error(const char* fmt, ...) {
     va_list ap;
@@ -22,6 +25,8 @@ void set_last_error(const char* fmt, ...) {
 template <typename TW>
 __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* __restrict__ tokens,
                                   float* __restrict__ out, int hidden, int vocab, int32_t* error_flag) {
+    dependents_may_launch();
+    wait_for_predecessor();
     const int row = blockIdx.x;
     const int tok = tokens[row];
     const bool ok = tok >= 0 && tok < vocab;
@@ -38,6 +43,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const TG* __restric
                                 const int32_t* __restrict__ row_index, TO* __restrict__ out,
                                 int hidden, float eps) {
     __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
     const int row = blockIdx.x;
     const float* src = x + (size_t)(row_index ? row_index[row] : row) * hidden;
     float ss = 0.0f;
@@ -54,6 +61,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const TG* __restric
 // act = g / (1 + exp(-g)) * u (reference: swiglu_kernel, kernels.cu:474-482).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int inter, int run) {
+    dependents_may_launch();
+    wait_for_predecessor();
     const int row = blockIdx.x;
     const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= inter) return;
@@ -69,11 +78,15 @@ using namespace citlali;
 
 extern "C" const char* citlali_last_error(void) { return g_last_error; }
 
+// 0: launch every kernel only after the one before it has finished; 1 (default): kernels may
+// start early and wait on the device for their predecessor (programmatic dependent launch).
+extern "C" void citlali_set_dependent_launch(int enabled) { g_dependent_launch = enabled != 0; }
+
 extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
                                   int rows, int hidden, int vocab, int32_t* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     return CITLALI_DISPATCH_FLOAT(table_dtype, TW, [&] {
-        embed_rows_kernel<TW><<<rows, 256, 0, stream>>>((const TW*)table, tokens, out, hidden, vocab, error_flag);
+        launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, error_flag);
         return CITLALI_LAUNCH_CHECK();
     });
 }
@@ -84,7 +97,7 @@ extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
         return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-            rms_norm_kernel<TG, TO><<<rows, threads, 0, stream>>>(x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
+            launch_kernel(rms_norm_kernel<TG, TO>, rows, threads, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
             return CITLALI_LAUNCH_CHECK();
         });
     });
@@ -103,7 +116,7 @@ extern "C" int citlali_swiglu(const void* gate_up, void* act, int dtype, int row
     }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         dim3 grid(rows, (inter + 255) / 256);
-        swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)gate_up, (T*)act, inter, run);
+        launch_kernel(swiglu_kernel<T>, grid, 256, 0, stream, (const T*)gate_up, (T*)act, inter, run);
         return CITLALI_LAUNCH_CHECK();
     });
 }

@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int M, int N, int K) {
     __shared__ float xs[kTileK][kTileM + 4];
     __shared__ float ws[kTileK][kTileN + 4];
+    dependents_may_launch();
+    wait_for_predecessor();
     const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * kTileN;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 4 x 4 outputs each
     float acc[4][4];
@@ -72,9 +74,9 @@ static int launch(const void* x, const void* w, void* y, int M, int N, int K, in
         return kTooLarge;
     }
     if (accumulate)
-        gemm_simt_kernel<TX, TW, TY, true><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (TY*)y, M, N, K);
+        launch_kernel(gemm_simt_kernel<TX, TW, TY, true>, grid, 256, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K);
     else
-        gemm_simt_kernel<TX, TW, TY, false><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, (TY*)y, M, N, K);
+        launch_kernel(gemm_simt_kernel<TX, TW, TY, false>, grid, 256, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K);
     return CITLALI_LAUNCH_CHECK();
 }
 

@@ -35,8 +35,11 @@ namespace tc {
 
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
 constexpr int kThreads = 192;
+constexpr int kMaxSplits = 16;
 
-enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kPartialF32 = 3 };
+enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
 struct GemmParams {
     void* out;             // [M, N] (or the partials' workspace [splits, M, N])
@@ -44,6 +47,8 @@ struct GemmParams {
     int M, N, K;           // the product's logical shape: y[M, N] = x[M, K] w[N, K]^T
     int rows_a, rows_b;    // rows of the 128-row operand and of the BN-row operand
     int splits;            // K is cut into this many ranges of whole 64-blocks
+    float* partials;       // split K: [tiles][splits][BN][128] float32
+    int* tile_counters;    // split K: one arrival counter per output tile, zero between launches
     int32_t* error_flag;
 };
 
@@ -54,7 +59,7 @@ constexpr int stages_for(bool swapped) {
 }
 
 template <int BN, bool kSwapped>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (kSwapped && BN <= 64) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int kStages = stages_for<BN>(kSwapped);
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
@@ -65,8 +70,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full_bar[kAccStages], acc_empty_bar[kAccStages];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_word;
+    __shared__ int last_flag;
     volatile int* abort_flag = &abort_word;
 
+    dependents_may_launch();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;            // tile storage starts on a 1024-byte boundary
     const uint32_t smem_a = tiles, smem_b = tiles + kStages * kBytesA;
@@ -102,25 +109,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                int ta, tb, sp;
-                decode(u, ta, tb, sp);
-                const int kb0 = sp * kb_per_split, kb1 = min(kblocks, kb0 + kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / kStages) & 1u) ^ 1u, abort_flag, p.error_flag, 101)) { ok = false; break; }
-                    const uint32_t bar = smem_u32(&full_bar[s]);
-                    mbar_arrive_expect_tx(bar, kBytesA + kBytesB);
-                    tma_load_2d(smem_a + s * kBytesA, &map_a, kb * kBK, ta * kBM, bar);
-                    tma_load_2d(smem_b + s * kBytesB, &map_b, kb * kBK, tb * BN, bar);
+            // Visit this block's (unit, K block) pairs in order; `body` returns false to stop.
+            auto for_each = [&](auto&& body) {
+                uint32_t it = 0;
+                for (int u = blockIdx.x; u < units; u += gridDim.x) {
+                    int ta, tb, sp;
+                    decode(u, ta, tb, sp);
+                    const int kb0 = sp * kb_per_split, kb1 = min(kblocks, kb0 + kb_per_split);
+                    for (int kb = kb0; kb < kb1; ++kb, ++it)
+                        if (!body(it, ta, tb, kb)) return it;
                 }
-            }
+                return it;
+            };
+            // The weights are written by no kernel, so the first ring of weight tiles is fetched before
+            // the kernel ahead of this one has finished; the rows of x only after it has.
+            auto load_weights = [&](int s, int ta, int tb, int kb, uint32_t bar) {
+                if (kSwapped) tma_load_2d(smem_a + s * kBytesA, &map_a, kb * kBK, ta * kBM, bar);
+                else tma_load_2d(smem_b + s * kBytesB, &map_b, kb * kBK, tb * BN, bar);
+            };
+            auto load_rows = [&](int s, int ta, int tb, int kb, uint32_t bar) {
+                if (kSwapped) tma_load_2d(smem_b + s * kBytesB, &map_b, kb * kBK, tb * BN, bar);
+                else tma_load_2d(smem_a + s * kBytesA, &map_a, kb * kBK, ta * kBM, bar);
+            };
+            const uint32_t early = for_each([&](uint32_t it, int ta, int tb, int kb) {
+                if (it >= (uint32_t)kStages) return false;
+                const uint32_t bar = smem_u32(&full_bar[it]);
+                mbar_arrive_expect_tx(bar, kBytesA + kBytesB);
+                load_weights(it, ta, tb, kb, bar);
+                return true;
+            });
+            wait_for_predecessor();
+            bool ok = true;
+            const uint32_t issued = for_each([&](uint32_t it, int ta, int tb, int kb) {
+                const int s = it % kStages;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                if (it < early) {
+                    load_rows(s, ta, tb, kb, bar);
+                    return true;
+                }
+                if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / kStages) & 1u) ^ 1u, abort_flag, p.error_flag, 101)) { ok = false; return false; }
+                mbar_arrive_expect_tx(bar, kBytesA + kBytesB);
+                load_weights(s, ta, tb, kb, bar);
+                load_rows(s, ta, tb, kb, bar);
+                return true;
+            });
             if (!ok) {
                 // leaving early: let the copies this thread issued land before shared memory goes away
-                const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0u;
-                for (uint32_t j = first; j < it; ++j) {
+                const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0u;
+                for (uint32_t j = first; j < issued; ++j) {
                     const uint32_t bar = smem_u32(&full_bar[j % kStages]);
                     const uint64_t start = global_timer();
                     while (!mbar_try_wait(bar, (j / kStages) & 1u) && global_timer() - start < 100000000ull) {}
@@ -157,6 +193,104 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
     } else {
         const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32 * quarter ..
+        float* outf = (float*)p.out;
+        __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
+        float gate_keep[16];
+        wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
+
+        // What becomes of 16 finished values: row i of the 128-row operand, rows j0 .. j0+15 of the other.
+        auto finish = [&](const float (&v)[16], int i, int j0, int c0) {
+            if (p.out_kind == kSwigluBF16) {
+                // Weight rows alternate in runs of 16: gate rows, then the up rows of the same outputs.
+                const int half_n = p.N >> 1;
+                if (kSwapped) {
+                    // lanes 0-15 of a warp hold gate values, lanes 16-31 the matching up values
+                    const int o_col = (i >> 5) * 16 + (lane & 15);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[c], 16);
+                        const int m = j0 + c;
+                        if ((lane & 16) == 0 && i < p.N && m < p.M)
+                            outh[(size_t)m * half_n + o_col] = __float2bfloat16_rn(silu_mul(v[c], other));
+                    }
+                } else if ((c0 & 16) == 0) {
+                    // this thread holds 16 consecutive columns: a gate run on even chunks, its up run on odd ones
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
+                } else if (i < p.M && j0 - 16 < p.N) {
+                    const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
+                    if (j0 + 16 <= p.N && (half_n % 8) == 0) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                                      silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
+                    }
+                }
+            } else if (kSwapped) {
+                // i is an output feature n, j a row m of x: out[m, n]; lanes hold consecutive n
+                if (i < p.N) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int m = j0 + c;
+                        if (m < p.M) {
+                            const size_t o = (size_t)m * p.N + i;
+                            if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[c]);
+                            else if (p.out_kind == kAddF32) outf[o] += v[c];
+                            else outf[o] = v[c];
+                        }
+                    }
+                }
+            } else if (i < p.M && j0 < p.N) {
+                // i is a row m of x, j an output feature n: this thread holds 16 consecutive n
+                const size_t o = (size_t)i * p.N + j0;
+                const bool full = j0 + 16 <= p.N;
+                if (p.out_kind == kStoreBF16) {
+                    if (full && (p.N % 8) == 0) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (j0 + c < p.N) outh[o + c] = __float2bfloat16_rn(v[c]);
+                    }
+                } else if (full && (p.N % 4) == 0) {
+                    float4* dst = reinterpret_cast<float4*>(outf + o);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float4 t = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        if (p.out_kind == kAddF32) {
+                            const float4 old = dst[c];
+                            t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+                        }
+                        dst[c] = t;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        if (j0 + c < p.N) {
+                            if (p.out_kind == kAddF32) outf[o + c] += v[c]; else outf[o + c] = v[c];
+                        }
+                }
+            }
+        };
+
         uint32_t acc_it = 0;
         for (int u = blockIdx.x; u < units; u += gridDim.x, ++acc_it) {
             int ta, tb, sp;
@@ -167,77 +301,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int i = ta * kBM + quarter * 32 + lane;     // row of the 128-row operand
             const bool empty_range = kb1 <= kb0;              // a split that got no K blocks contributes zeros
-            float* outf = (float*)p.out;
-            __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
-            if (p.out_kind == kPartialF32) outf += (size_t)sp * p.M * p.N;
+            // split K: element (i, j) of split sp lives at partials[sp][i_local][j_local] of its tile, lanes contiguous
+            const size_t tile_elems = (size_t)kBM * BN;
+            float* part = p.partials + ((size_t)(tb * tiles_a + ta) * p.splits) * tile_elems;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r);
                 tmem_ld_wait();
-                if (empty_range) {
+                float v[16];
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) r[c] = 0u;
-                }
-                const int j0 = tb * BN + c0;                  // first row of the BN-row operand in this chunk
-                if (kSwapped) {
-                    // i is an output feature n, j a row m of x: out[m, n]; lanes hold consecutive n
-                    if (i < p.N) {
+                for (int c = 0; c < 16; ++c) v[c] = empty_range ? 0.0f : __uint_as_float(r[c]);
+                if (p.splits > 1) {
+                    float* dst = part + (size_t)sp * tile_elems + (size_t)c0 * kBM + quarter * 32 + lane;
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int m = j0 + c;
-                            if (m < p.M) {
-                                const size_t o = (size_t)m * p.N + i;
-                                const float v = __uint_as_float(r[c]);
-                                if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v);
-                                else if (p.out_kind == kAddF32) outf[o] += v;
-                                else outf[o] = v;
-                            }
-                        }
-                    }
+                    for (int c = 0; c < 16; ++c) __stcg(dst + (size_t)c * kBM, v[c]);
                 } else {
-                    // i is a row m of x, j an output feature n: this thread holds 16 consecutive n
-                    if (i < p.M && j0 < p.N) {
-                        const size_t o = (size_t)i * p.N + j0;
-                        const bool full = j0 + 16 <= p.N;
-                        if (p.out_kind == kStoreBF16) {
-                            if (full && (p.N % 8) == 0) {
-                                uint32_t w[8];
-#pragma unroll
-                                for (int c = 0; c < 8; ++c) {
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1]));
-                                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                                }
-                                uint4* dst = reinterpret_cast<uint4*>(outh + o);
-                                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                            } else {
-                                for (int c = 0; c < 16 && j0 + c < p.N; ++c) outh[o + c] = __float2bfloat16_rn(__uint_as_float(r[c]));
-                            }
-                        } else if (full && (p.N % 4) == 0) {
-                            float4* dst = reinterpret_cast<float4*>(outf + o);
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                float4 v = make_float4(__uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]),
-                                                       __uint_as_float(r[4 * c + 2]), __uint_as_float(r[4 * c + 3]));
-                                if (p.out_kind == kAddF32) {
-                                    const float4 old = dst[c];
-                                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                                }
-                                dst[c] = v;
-                            }
-                        } else {
-                            for (int c = 0; c < 16 && j0 + c < p.N; ++c) {
-                                const float v = __uint_as_float(r[c]);
-                                if (p.out_kind == kAddF32) outf[o + c] += v; else outf[o + c] = v;
-                            }
-                        }
-                    }
+                    finish(v, i, tb * BN + c0, c0);
                 }
             }
+            // the accumulator stage is free again
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[as]));
+            if (p.splits > 1) {
+                // The block that brings a tile's last partial adds all of them, in split order, and
+                // finishes the tile.  Which block that is varies; the order of the sum does not.
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    int* counter = p.tile_counters + (tb * tiles_a + ta);
+                    const int arrived = atomicAdd(counter, 1);
+                    last_flag = (arrived == p.splits - 1) ? 1 : 0;
+                    if (last_flag) *counter = 0;               // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (last_flag) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        float v[16];
+                        // four columns at a time: every split's loads are issued before the first addition,
+                        // then added in split order
+#pragma unroll
+                        for (int cg = 0; cg < 16; cg += 4) {
+                            const float* src = part + (size_t)(c0 + cg) * kBM + quarter * 32 + lane;
+                            float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+                            for (int z0 = 0; z0 < p.splits; z0 += 4) {
+                                float t[4][4];
+#pragma unroll
+                                for (int z = 0; z < 4; ++z)
+#pragma unroll
+                                    for (int k = 0; k < 4; ++k)
+                                        t[z][k] = z0 + z < p.splits ? __ldcg(src + (size_t)(z0 + z) * tile_elems + (size_t)k * kBM) : 0.0f;
+#pragma unroll
+                                for (int z = 0; z < 4; ++z)
+#pragma unroll
+                                    for (int k = 0; k < 4; ++k) a[k] += t[z][k];
+                            }
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) v[cg + k] = a[k];
+                        }
+                        finish(v, i, tb * BN + c0, c0);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is read by all before it is rewritten
+            }
         }
     }
 
@@ -247,18 +377,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-}
-
-// out (+)= sum over splits of partials, in split order.
-__global__ void splitk_reduce_kernel(const float* __restrict__ partials, void* __restrict__ out, int out_kind,
-                                     size_t elements, int splits) {
-    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= elements) return;
-    float s = partials[e];
-    for (int z = 1; z < splits; ++z) s += partials[(size_t)z * elements + e];
-    if (out_kind == kStoreBF16) ((__nv_bfloat16*)out)[e] = __float2bfloat16_rn(s);
-    else if (out_kind == kAddF32) ((float*)out)[e] += s;
-    else ((float*)out)[e] = s;
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -309,7 +427,7 @@ struct Plan {
 
 // The plan is a function of the shape alone.  Swapped up to 128 rows of x; the split aims at
 // two blocks on every SM and keeps at least four K blocks per block.
-static Plan make_plan(int M, int N, int K, int sm_count) {
+static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
     Plan pl;
     pl.swapped = M <= 128;
     if (pl.swapped) {
@@ -318,8 +436,9 @@ static Plan make_plan(int M, int N, int K, int sm_count) {
         const int kblocks = (K + kBK - 1) / kBK;
         const int slots = sm_count * (pl.bn <= 64 ? 2 : 1);
         int s = slots / tiles;
+        if (force_splits > 0) s = force_splits;
         if (s > kblocks / 4) s = kblocks / 4;
-        if (s > 16) s = 16;
+        if (s > kMaxSplits) s = kMaxSplits;
         if (s < 1) s = 1;
         pl.splits = s;
     } else {
@@ -344,7 +463,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     const int units = tiles_a * tiles_b * p.splits;
     const int per_sm = (kSwapped && BN <= 64) ? 2 : 1;
     const int grid = units < sm_count * per_sm ? units : sm_count * per_sm;
-    kernel<<<grid, kThreads, smem, stream>>>(ma, mb, p);
+    launch_kernel(kernel, grid, kThreads, smem, stream, ma, mb, p);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -354,24 +473,42 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 using namespace citlali;
 using namespace citlali::tc;
 
-// How the product of this shape would run: *swapped, *bn, *splits, and the bytes of float32
-// scratch it needs for split-K partials (0 if it does not split).
-extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int* swapped, int* bn, int* splits,
-                                    size_t* workspace_bytes) {
-    Plan pl = make_plan(M, N, K, sm_count);
+static size_t partial_bytes(const Plan& pl, int M, int N) {
+    if (pl.splits <= 1) return 0;
+    const int rows_a = pl.swapped ? N : M, rows_b = pl.swapped ? M : N;
+    const size_t tiles = (size_t)((rows_a + kBM - 1) / kBM) * ((rows_b + pl.bn - 1) / pl.bn);
+    return tiles * pl.splits * kBM * pl.bn * sizeof(float);
+}
+
+// How the product of this shape would run: *swapped, *bn, *splits, the bytes of float32 scratch
+// it needs for split-K partials (0 if it does not split) and the number of tile counters.
+extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits,
+                                    size_t* workspace_bytes, int* tile_counters) {
+    if (sm_count <= 0) sm_count = 148;
+    Plan pl = make_plan(M, N, K, sm_count, force_splits);
     if (swapped) *swapped = pl.swapped;
     if (bn) *bn = pl.bn;
     if (splits) *splits = pl.splits;
-    if (workspace_bytes) *workspace_bytes = pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0;
+    if (workspace_bytes) *workspace_bytes = partial_bytes(pl, M, N);
+    if (tile_counters) {
+        const int rows_a = pl.swapped ? N : M, rows_b = pl.swapped ? M : N;
+        *tile_counters = pl.splits > 1 ? ((rows_a + kBM - 1) / kBM) * ((rows_b + pl.bn - 1) / pl.bn) : 0;
+    }
     return 0;
 }
 
-// y[M, N] (y_dtype: 0 float32, 1 bfloat16) = x . w^T, or with accumulate != 0: y (float32) += x . w^T.
-// x [M, K] and w [N, K] are bfloat16, contiguous, 16-byte aligned, K a multiple of 8.
-// `workspace` must hold what citlali_gemm_tc_plan reports for this shape.
+// y = x . w^T with x [M, K] and w [N, K] bfloat16, contiguous, 16-byte aligned, K a multiple of 8.
+// `mode` bits: 1 = y (float32 [M, N]) += product; 2 = SiLU-gate epilogue: w's rows alternate in runs
+// of 16 between gate and up rows and y is bfloat16 [M, N/2] = silu(gate) * up (N a multiple of 32).
+// Without them y is [M, N] of y_dtype (0 float32, 1 bfloat16).  When the shape splits K (see
+// citlali_gemm_tc_plan), `workspace` must hold the reported bytes and `tile_counters` the reported
+// number of ints, all zero: every block writes its partial there, and the block that brings a
+// tile's last partial adds them in split order and writes the tile; the counters are zero again
+// when the kernel ends.  `force_splits` > 0 replaces the plan's K split (for tuning and tests).
 extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
-                               int accumulate, void* workspace, size_t workspace_bytes, int32_t* error_flag,
-                               int sm_count, cudaStream_t stream) {
+                               int mode, int force_splits, void* workspace, size_t workspace_bytes, int* tile_counters,
+                               int counters_len, int32_t* error_flag, int sm_count, cudaStream_t stream) {
+    const bool accumulate = (mode & 1) != 0, swiglu = (mode & 2) != 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) {
         set_last_error("gemm_tc: the inner size %d must be a positive multiple of 8 (rows of 16-byte multiples for TMA)", K);
@@ -389,30 +526,37 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
         set_last_error("gemm_tc: output dtype code %d is neither float32 nor bfloat16", y_dtype);
         return kBadDType;
     }
+    if (swiglu && (accumulate || y_dtype != kBF16 || N % 32 != 0)) {
+        set_last_error("gemm_tc: the gate epilogue needs a bfloat16 output and N a multiple of 32 (N %d)", N);
+        return kBadShape;
+    }
     if (sm_count <= 0) sm_count = 148;
-    const Plan pl = make_plan(M, N, K, sm_count);
-    const int final_kind = accumulate ? kAddF32 : (y_dtype == kF32 ? kStoreF32 : kStoreBF16);
+    const Plan pl = make_plan(M, N, K, sm_count, force_splits);
     GemmParams p;
     p.M = M; p.N = N; p.K = K;
     p.splits = pl.splits;
     p.error_flag = error_flag;
+    p.out = y;
+    p.out_kind = swiglu ? kSwigluBF16 : accumulate ? kAddF32 : (y_dtype == kF32 ? kStoreF32 : kStoreBF16);
+    p.partials = nullptr;
+    p.tile_counters = nullptr;
+    p.rows_a = pl.swapped ? N : M;
+    p.rows_b = pl.swapped ? M : N;
     if (pl.splits > 1) {
-        const size_t need = (size_t)pl.splits * M * N * sizeof(float);
-        if (workspace == nullptr || workspace_bytes < need) {
-            set_last_error("gemm_tc: a [%d, %d, %d] product splits K %d ways and needs %zu bytes of scratch, %zu were given",
-                           M, N, K, pl.splits, need, workspace_bytes);
+        const size_t need = partial_bytes(pl, M, N);
+        const int tiles = ((p.rows_a + kBM - 1) / kBM) * ((p.rows_b + pl.bn - 1) / pl.bn);
+        if (workspace == nullptr || workspace_bytes < need || tile_counters == nullptr || counters_len < tiles) {
+            set_last_error("gemm_tc: a [%d, %d, %d] product splits K %d ways and needs %zu bytes of scratch and %d tile "
+                           "counters; %zu bytes and %d counters were given", M, N, K, pl.splits, need, tiles,
+                           workspace_bytes, counters_len);
             return kTooLarge;
         }
-        p.out = workspace;
-        p.out_kind = kPartialF32;
-    } else {
-        p.out = y;
-        p.out_kind = final_kind;
+        p.partials = (float*)workspace;
+        p.tile_counters = tile_counters;
     }
     CUtensorMap ma, mb;
     int rc;
     if (pl.swapped) {
-        p.rows_a = N; p.rows_b = M;
         if ((rc = make_map(&ma, w, N, K, kBM))) return rc;
         if ((rc = make_map(&mb, x, M, K, pl.bn))) return rc;
         switch (pl.bn) {
@@ -422,18 +566,10 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
             default: rc = launch<128, true>(ma, mb, p, sm_count, stream); break;
         }
     } else {
-        p.rows_a = M; p.rows_b = N;
         if ((rc = make_map(&ma, x, M, K, kBM))) return rc;
         if ((rc = make_map(&mb, w, N, K, pl.bn))) return rc;
         if (pl.bn == 256) rc = launch<256, false>(ma, mb, p, sm_count, stream);
         else rc = launch<128, false>(ma, mb, p, sm_count, stream);
     }
-    if (rc) return rc;
-    if (pl.splits > 1) {
-        const size_t elements = (size_t)M * N;
-        splitk_reduce_kernel<<<(unsigned)((elements + 255) / 256), 256, 0, stream>>>((const float*)workspace, y, final_kind,
-                                                                                    elements, pl.splits);
-        return CITLALI_LAUNCH_CHECK();
-    }
-    return 0;
+    return rc;
 }

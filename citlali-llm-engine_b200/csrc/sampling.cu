@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ tokens, int vocab) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    dependents_may_launch();
+    wait_for_predecessor();
     float best;
     int best_id;
     block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, best, best_id, sv, si);
@@ -66,6 +68,8 @@ sample_rows_kernel(const float* __restrict__ logits, const float* __restrict__ t
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float seg_sum[32];
+    dependents_may_launch();
+    wait_for_predecessor();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     const float temp = temperature[blockIdx.x];
     float best;
@@ -129,7 +133,7 @@ extern "C" int citlali_argmax_rows(const float* logits, int32_t* tokens, int row
         set_last_error("argmax_rows: vocabulary size %d must be positive", vocab);
         return kBadShape;
     }
-    argmax_rows_kernel<<<rows, 1024, 0, stream>>>(logits, tokens, vocab);
+    launch_kernel(argmax_rows_kernel, rows, 1024, 0, stream, logits, tokens, vocab);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -140,6 +144,6 @@ extern "C" int citlali_sample_rows(const float* logits, const float* temperature
         set_last_error("sample_rows: vocabulary size %d must be positive", vocab);
         return kBadShape;
     }
-    sample_rows_kernel<<<rows, 1024, 0, stream>>>(logits, temperature, uniform, tokens, vocab);
+    launch_kernel(sample_rows_kernel, rows, 1024, 0, stream, logits, temperature, uniform, tokens, vocab);
     return CITLALI_LAUNCH_CHECK();
 }

@@ -47,7 +47,7 @@ def _stream():
 
 
 _launches = 0
-_KERNELS_PER_CALL = {"gemm_tc": 1, "attention_decode": 2}
+_KERNELS_PER_CALL = {"attention_decode": 2}
 
 
 def launch_count() -> int:
@@ -230,13 +230,14 @@ def sm_count(device) -> int:
     return _sm_count[idx]
 
 
-def gemm_tc_plan(M: int, N: int, K: int, device) -> dict:
-    """How the tensor-core product of this shape runs, and the scratch bytes it needs."""
-    swapped, bn, splits = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+def gemm_tc_plan(M: int, N: int, K: int, device, force_splits: int = 0) -> dict:
+    """How the tensor-core product of this shape runs, and the scratch it needs when it splits K."""
+    swapped, bn, splits, counters = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     need = ctypes.c_size_t()
-    lib().citlali_gemm_tc_plan(_i(M), _i(N), _i(K), _i(sm_count(device)), ctypes.byref(swapped), ctypes.byref(bn),
-                               ctypes.byref(splits), ctypes.byref(need))
-    return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value, "workspace_bytes": need.value}
+    lib().citlali_gemm_tc_plan(_i(M), _i(N), _i(K), _i(sm_count(device)), _i(force_splits), ctypes.byref(swapped), ctypes.byref(bn),
+                               ctypes.byref(splits), ctypes.byref(need), ctypes.byref(counters))
+    return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value, "workspace_bytes": need.value,
+            "tile_counters": counters.value}
 
 
 def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
@@ -256,6 +257,22 @@ def _gemm_workspace(device, nbytes: int) -> torch.Tensor:
     return _scratch(device, "gemm split-K", nbytes)
 
 
+_counters = {}
+
+
+def _gemm_counters(device, count: int) -> torch.Tensor:
+    """Arrival counters of the split-K product's output tiles: zero between launches (the kernel
+    leaves them so)."""
+    key = torch.device(device).index or 0
+    c = _counters.get(key)
+    if c is None or c.numel() < count:
+        require(not torch.cuda.is_current_stream_capturing(),
+                "the tile counters would have to grow during graph capture; run the step once before capturing")
+        c = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _counters[key] = c
+    return c
+
+
 def gemm_tc_accepts(x, w, y) -> bool:
     """The tensor-core product's shape rules: bfloat16 operands, an inner size that is a
     multiple of 8 (TMA needs rows of 16-byte multiples), 16-byte aligned starts."""
@@ -264,17 +281,23 @@ def gemm_tc_accepts(x, w, y) -> bool:
             and x.is_contiguous() and w.is_contiguous() and y.is_contiguous())
 
 
-def gemm_tc(x, w, y, accumulate=False, error_flag=None):
+def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_splits=0):
+    """``y = x . w^T`` on the tensor cores.  ``accumulate``: ``y`` (float32) ``+=``.  ``swiglu``: ``w``'s
+    rows alternate gate/up in runs of 16 and ``y`` is bfloat16 ``[M, N/2] = silu(gate) * up``."""
     _need_cuda(x, w, y, error_flag)
-    require(gemm_tc_accepts(x, w, y), "gemm_tc: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
     M, K = x.shape
     N = w.shape[0]
-    require(w.shape[1] == K and y.shape == (M, N), "gemm_tc: shapes do not fit")
-    need = gemm_tc_plan(M, N, K, x.device)["workspace_bytes"]
-    ws = _gemm_workspace(x.device, need) if need else None
-    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K),
-                                 _i(1 if accumulate else 0), _ptr(ws), ctypes.c_size_t(ws.numel() if ws is not None else 0),
-                                 _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")
-    if need:
-        global _launches
-        _launches += 1          # the split-K reduction
+    require(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and w.shape[1] == K
+            and x.is_contiguous() and w.is_contiguous(),
+            "gemm_tc: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
+    require(y.shape == (M, N // 2 if swiglu else N), "gemm_tc: the output's shape does not fit")
+    plan = gemm_tc_plan(M, N, K, x.device, force_splits)
+    ws = counters = None
+    if plan["splits"] > 1:
+        ws = _gemm_workspace(x.device, plan["workspace_bytes"])
+        counters = _gemm_counters(x.device, plan["tile_counters"])
+    mode = (1 if accumulate else 0) | (2 if swiglu else 0)
+    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode), _i(force_splits), _ptr(ws),
+                                 ctypes.c_size_t(ws.numel() if ws is not None else 0), _ptr(counters),
+                                 _i(counters.numel() if counters is not None else 0), _ptr(error_flag),
+                                 _i(sm_count(x.device)), _stream()), "gemm_tc")

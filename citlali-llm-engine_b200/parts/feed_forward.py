@@ -37,9 +37,10 @@ class GatedSiluFeedForward:
         self.dtype = ctx.dtype
 
     def forward(self, h, batch, residual):
-        gu = self.gate_up.forward(h)
-        act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
-        ops.swiglu(gu, act, self.run)
+        act = self.gate_up.forward_gated(h, self.run)              # gate in the product's epilogue
+        if act is None:
+            act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
+            ops.swiglu(self.gate_up.forward(h), act, self.run)
         self.down.forward(act, accumulate_into=residual)
         return residual
 

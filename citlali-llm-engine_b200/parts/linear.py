@@ -66,6 +66,20 @@ class DenseLinear:
         self.weight = weight
         self.dtype = dtype
 
+    def uses_tensor_cores(self, x: torch.Tensor) -> bool:
+        return (self.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.in_features % 8 == 0
+                and x.is_contiguous() and x.data_ptr() % 16 == 0)
+
+    def forward_gated(self, x: torch.Tensor, run: int):
+        """For two stacked matrices interleaved in runs of 16 (gate, up): ``silu(gate) * up`` straight
+        from the product's epilogue, or ``None`` if this shape cannot (call :meth:`forward`)."""
+        rows = x.shape[0]
+        if rows == 0 or run != 16 or self.out_features % 32 != 0 or not self.uses_tensor_cores(x):
+            return None
+        act = torch.empty((rows, self.out_features // 2), dtype=torch.bfloat16, device=x.device)
+        ops.gemm_tc(x, self.weight, act, error_flag=self.error_flag, swiglu=True)
+        return act
+
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``accumulate_into`` (float32 [rows, out]) receives ``+= x . W^T`` and is returned;

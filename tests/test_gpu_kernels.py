@@ -397,3 +397,33 @@ def test_attention_prefill_flash(nq, nkv, d, window):
     if window == 0:
         assert (out[starts[5] + 250].view(nq, d)[0].double().cpu() - v[5][11, 0]).abs().max() < 0.1
     assert not ops.lib().citlali_attention_prefill_supports(40, 64) and not ops.lib().citlali_attention_prefill_supports(128, 16)
+
+
+@pytest.mark.parametrize("M,inter,K", [(1, 192, 64), (8, 12288, 512), (70, 160, 96), (128, 48, 64), (129, 64, 128),
+                                       (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024)])
+def test_gemm_tc_gate_epilogue(M, inter, K):
+    """silu(gate) * up straight from the product's epilogue, in both forms and with K split."""
+    g = torch.Generator().manual_seed(M + inter)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(inter, K, generator=g) * 0.2).to(torch.bfloat16); wu = (torch.randn(inter, K, generator=g) * 0.2).to(torch.bfloat16)
+    want = plain.swiglu(x.double() @ wg.double().t(), x.double() @ wu.double().t())
+    packed = torch.stack([wg.view(-1, 16, K), wu.view(-1, 16, K)], dim=1).reshape(2 * inter, K).contiguous()
+    act = torch.empty(M, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x.to(DEV), packed.to(DEV), act, swiglu=True)
+    close(act, want, torch.bfloat16)
+    with pytest.raises(cb.CitlaliError, match="gate epilogue"):
+        ops.gemm_tc(x.to(DEV), packed[:2 * inter - 16].contiguous().to(DEV), torch.empty(M, inter - 8, dtype=torch.bfloat16, device=DEV), swiglu=True)
+
+
+def test_gemm_tc_split_k_leaves_its_counters_zero():
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(8, 4096, generator=g).to(torch.bfloat16).to(DEV); w = torch.randn(4096, 4096, generator=g).to(torch.bfloat16).to(DEV)
+    assert ops.gemm_tc_plan(8, 4096, 4096, DEV)["splits"] > 1
+    y = torch.empty(8, 4096, device=DEV)
+    outs = []
+    for _ in range(3):
+        ops.gemm_tc(x, w, y)
+        outs.append(y.clone())
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])       # the same sum order every time
+    assert int(ops._counters[0].abs().sum()) == 0
