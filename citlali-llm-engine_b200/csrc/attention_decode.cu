@@ -17,7 +17,8 @@
 
 namespace citlali {
 
-constexpr int kChunkPages = 4;     // pages per block
+constexpr int kChunkPages = 4;     // pages per block of the CUDA-core kernel
+constexpr int kKvStages = 3;       // key/value tiles in flight per block of the tensor-core kernel, plus the one in use
 constexpr int kDecodeWarps = 4;
 
 // EPL consecutive bfloat16 of a key row and of a value row, widened to float, with one load each.
@@ -213,7 +214,8 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                            const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                            const int32_t* __restrict__ page_table, int page_table_stride,
                            const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
-                           float* __restrict__ partial, int max_chunks, int nq, int nkv, int window, float scale_log2) {
+                           float* __restrict__ partial, int max_chunks, int chunk_pages, int nq, int nkv, int window,
+                           float scale_log2) {
     using namespace fa;
     constexpr int kPage = 64;
     constexpr int kRowBytes = D * 2 + 16;
@@ -221,7 +223,7 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     constexpr int kChunksPerRow = D / 8;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);          // 16 rows
-    const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + 2 * kTileBytes;
+    const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + kKvStages * kTileBytes;
 
     dependents_may_launch();
     wait_for_predecessor();
@@ -234,9 +236,9 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int row = blockIdx.z;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int chunk_keys = kChunkPages * kPage;
+    const int chunk_keys = chunk_pages * kPage;
     if (chunk * chunk_keys > pos || chunk * chunk_keys + chunk_keys <= lo) return;
-    const int tile_lo = max(chunk * kChunkPages, lo / kPage), tile_hi = min(chunk * kChunkPages + kChunkPages - 1, pos / kPage);
+    const int tile_lo = max(chunk * chunk_pages, lo / kPage), tile_hi = min(chunk * chunk_pages + chunk_pages - 1, pos / kPage);
     const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -257,9 +259,11 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     };
     load_tile(tile_lo, 0);
     cp_async_commit();
+    if (tile_lo + 1 <= tile_hi) load_tile(tile_lo + 1, 1);
+    cp_async_commit();
 
     uint32_t qf[D / 16][4];
-    cp_async_wait<1>();
+    cp_async_wait<2>();
     __syncthreads();
     {
         const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -274,10 +278,10 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
     for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-        const int buf = (tile - tile_lo) & 1;
-        if (tile + 1 <= tile_hi) load_tile(tile + 1, buf ^ 1);
+        const int buf = (tile - tile_lo) % kKvStages;
+        if (tile + 2 <= tile_hi) load_tile(tile + 2, (tile + 2 - tile_lo) % kKvStages);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<2>();
         __syncthreads();
         const uint32_t kb = s_k + buf * kTileBytes + warp * 16 * kRowBytes, vb = s_v + buf * kTileBytes + warp * 16 * kRowBytes;
         float s[2][4];
@@ -373,8 +377,8 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 template <int D>
 static int launch_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                      int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, float* partial,
-                     int max_chunks, int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
-    constexpr int tiles = (16 + 4 * 64) * (D * 2 + 16);
+                     int max_chunks, int chunk_pages, int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
+    constexpr int tiles = (16 + 2 * kKvStages * 64) * (D * 2 + 16);
     constexpr int park = 16 * (D * 2 + 16) + 4 * 16 * (D + 2) * 4;
     constexpr int smem = tiles > park ? tiles : park;
     auto kernel = attention_decode_tc_kernel<D>;
@@ -388,7 +392,7 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
     dim3 grid(max_chunks, nkv * ((group + 15) / 16), rows);
     launch_kernel(kernel, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                         (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
-                                        partial, max_chunks, nq, nkv, window, scale * 1.4426950408889634f);
+                                        partial, max_chunks, chunk_pages, nq, nkv, window, scale * 1.4426950408889634f);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -430,7 +434,7 @@ using namespace citlali;
 // Scratch for the partials of `rows` single-token rows whose positions stay below
 // `max_positions`: floats.
 extern "C" size_t citlali_attention_decode_scratch_floats(int rows, int nq, int head_dim, int page_size, int max_positions) {
-    const int chunk_keys = kChunkPages * page_size;
+    const int chunk_keys = 2 * page_size;                     // the smallest chunk any kernel here uses
     const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;
     return (size_t)rows * nq * max_chunks * (head_dim + 2);
 }
@@ -457,18 +461,35 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         set_last_error("attention_decode: %d rows or %d heads exceed the grid limit", rows, nq);
         return kTooLarge;
     }
-    const int chunk_keys = kChunkPages * page_size;
+    const int group = nq / nkv;
+    bool tensor_cores = page_size == 64 && q_stride % 8 == 0 && (((uintptr_t)q) & 15u) == 0;
+    switch (head_dim) {
+        case 16: case 32: case 48: case 64: case 80: case 96: case 112: case 128: case 256: break;
+        default: tensor_cores = false;
+    }
+    // Pages per block.  The tensor-core kernel takes the smallest of 2, 4, 8, 16 that keeps the grid
+    // near two waves: few sequences get short chunks (enough blocks to fill the GPU), many sequences
+    // long ones (less merging).  The choice depends on the batch and the longest possible context
+    // only, not on the sequences' lengths, so a captured launch stays valid.
+    int chunk_pages = kChunkPages;
+    if (tensor_cores) {
+        const int kv_tiles = nkv * ((group + 15) / 16);
+        const int max_pages = (max_positions + page_size - 1) / page_size;
+        chunk_pages = 16;
+        for (int c = 2; c <= 16; c *= 2)
+            if ((long long)rows * kv_tiles * ((max_pages + c - 1) / c) <= 600) { chunk_pages = c; break; }
+    }
+    const int chunk_keys = chunk_pages * page_size;
     const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;
-    const size_t need = citlali_attention_decode_scratch_floats(rows, nq, head_dim, page_size, max_positions);
+    const size_t need = (size_t)rows * nq * max_chunks * (head_dim + 2);
     if (partial == nullptr || partial_floats < need) {
         set_last_error("attention_decode: %zu floats of scratch are needed, %zu were given", need, partial_floats);
         return kTooLarge;
     }
-    const int group = nq / nkv;
     int rc = -1000;
-    if (page_size == 64 && q_stride % 8 == 0 && (((uintptr_t)q) & 15u) == 0) {
+    if (tensor_cores) {
 #define CITLALI_TC(DD) case DD: rc = launch_tc<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, \
-                                                    partial, max_chunks, rows, nq, nkv, window, scale, stream); break
+                                                    partial, max_chunks, chunk_pages, rows, nq, nkv, window, scale, stream); break
         switch (head_dim) {
             CITLALI_TC(16); CITLALI_TC(32); CITLALI_TC(48); CITLALI_TC(64); CITLALI_TC(80); CITLALI_TC(96); CITLALI_TC(112);
             CITLALI_TC(128); CITLALI_TC(256);

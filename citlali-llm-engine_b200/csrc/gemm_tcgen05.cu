@@ -338,32 +338,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (last_flag) {
                     __threadfence();
+                    // Only the swapped form splits K: the tile's 128 rows are output features n, its BN
+                    // columns are rows m of x, and partials lie [split][m][n] with n contiguous.  An item is
+                    // four consecutive n of one m; the 128 epilogue threads share the tile's BN * 32 items.
+                    const int et = threadIdx.x - 64;
+                    const int n_tile = ta * kBM, m_tile = tb * BN;
+                    const int half_n = p.N >> 1;
+                    const bool gate = p.out_kind == kSwigluBF16;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        float v[16];
-                        // four columns at a time: every split's loads are issued before the first addition,
-                        // then added in split order
-#pragma unroll
-                        for (int cg = 0; cg < 16; cg += 4) {
-                            const float* src = part + (size_t)(c0 + cg) * kBM + quarter * 32 + lane;
-                            float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    for (int item = et; item < BN * 32; item += 128) {
+                        const int c = item >> 5, l4 = item & 31;
+                        const int m = m_tile + c, n0 = n_tile + 4 * l4;
+                        if (m >= p.M || n0 >= p.N) continue;
+                        if (gate && (l4 & 4)) continue;                 // an up run: done with its gate run
+                        const float* src = part + (size_t)c * kBM + 4 * l4;
+                        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-                            for (int z0 = 0; z0 < p.splits; z0 += 4) {
-                                float t[4][4];
+                        for (int z0 = 0; z0 < p.splits; z0 += 8) {
+                            float4 t[8], tu[8];
 #pragma unroll
-                                for (int z = 0; z < 4; ++z)
-#pragma unroll
-                                    for (int k = 0; k < 4; ++k)
-                                        t[z][k] = z0 + z < p.splits ? __ldcg(src + (size_t)(z0 + z) * tile_elems + (size_t)k * kBM) : 0.0f;
-#pragma unroll
-                                for (int z = 0; z < 4; ++z)
-#pragma unroll
-                                    for (int k = 0; k < 4; ++k) a[k] += t[z][k];
+                            for (int z = 0; z < 8; ++z) {
+                                const bool on = z0 + z < p.splits;
+                                t[z] = on ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z0 + z) * tile_elems))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (gate)
+                                    tu[z] = on ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z0 + z) * tile_elems + 16))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
                             }
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) v[cg + k] = a[k];
+                            for (int z = 0; z < 8; ++z) {
+                                a.x += t[z].x; a.y += t[z].y; a.z += t[z].z; a.w += t[z].w;
+                                if (gate) { u.x += tu[z].x; u.y += tu[z].y; u.z += tu[z].z; u.w += tu[z].w; }
+                            }
                         }
-                        finish(v, i, tb * BN + c0, c0);
+                        const float v[4] = {a.x, a.y, a.z, a.w};
+                        if (gate) {
+                            const float uu[4] = {u.x, u.y, u.z, u.w};
+                            const size_t o = (size_t)m * half_n + (n0 >> 5) * 16 + (n0 & 15);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                if (n0 + k < p.N) outh[o + k] = __float2bfloat16_rn(silu_mul(v[k], uu[k]));
+                        } else {
+                            const size_t o = (size_t)m * p.N + n0;
+                            if (n0 + 4 <= p.N && (p.N & 3) == 0) {
+                                if (p.out_kind == kStoreBF16) {
+                                    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                                    *reinterpret_cast<uint2*>(outh + o) =
+                                        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                                } else {
+                                    float4 w = a;
+                                    if (p.out_kind == kAddF32) {
+                                        const float4 old = *reinterpret_cast<const float4*>(outf + o);
+                                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                                    }
+                                    *reinterpret_cast<float4*>(outf + o) = w;
+                                }
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 4; ++k)
+                                    if (n0 + k < p.N) {
+                                        if (p.out_kind == kStoreBF16) outh[o + k] = __float2bfloat16_rn(v[k]);
+                                        else if (p.out_kind == kAddF32) outf[o + k] += v[k];
+                                        else outf[o + k] = v[k];
+                                    }
+                            }
+                        }
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is read by all before it is rewritten
@@ -436,6 +475,9 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
         const int kblocks = (K + kBK - 1) / kBK;
         const int slots = sm_count * (pl.bn <= 64 ? 2 : 1);
         int s = slots / tiles;
+        // partials are written and read once each: keep them under a quarter of the weights' bytes
+        const int traffic_cap = K / (16 * pl.bn);
+        if (s > traffic_cap) s = traffic_cap;
         if (force_splits > 0) s = force_splits;
         if (s > kblocks / 4) s = kblocks / 4;
         if (s > kMaxSplits) s = kMaxSplits;

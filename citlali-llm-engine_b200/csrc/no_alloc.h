@@ -14,7 +14,7 @@
 // library instead of being passed in.
 //
 //   Limit.  The array holds CITLALI_NO_ALLOC_SCRATCH_FLOATS floats (4 MiB).  A call needs
-//   rows * nq * ceil(max_positions / (4 * page_size)) * (head_dim + 2) floats; a call that
+//   rows * nq * ceil(max_positions / (2 * page_size)) * (head_dim + 2) floats; a call that
 //   needs more is refused with a negative return code and a message (citlali_last_error),
 //   and nothing is launched.  Every GPU that loads the library holds these 4 MiB until the
 //   process exits.
