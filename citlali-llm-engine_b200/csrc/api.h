@@ -77,6 +77,9 @@ int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, c
 
 // tokens[r] = argmax of logits[r, :] over finite values, lowest index on ties.
 int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int vocab, cudaStream_t stream);
+// The same with 64 blocks per row; scratch holds rows * 128 floats.
+int citlali_argmax_rows_wide(const float* logits, int32_t* tokens, float* scratch, int rows, int vocab,
+                             cudaStream_t stream);
 
 // tokens[r] = first index whose inclusive CDF of softmax(logits[r] / temperature[r]) exceeds
 // uniform[r]; temperature[r] <= 0 means argmax.

@@ -58,6 +58,57 @@ argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ token
     if (threadIdx.x == 0) tokens[blockIdx.x] = best_id;
 }
 
+// The same in two steps for large vocabularies: each block scans one segment of a row, then one
+// small block per row picks among the segments (lowest index on ties, as in a single scan).
+constexpr int kArgmaxSegments = 64;
+
+__global__ void __launch_bounds__(256)
+argmax_segments_kernel(const float* __restrict__ logits, float* __restrict__ seg_value, int* __restrict__ seg_index, int vocab) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.y, seg = blockIdx.x;
+    const int len = (vocab + kArgmaxSegments - 1) / kArgmaxSegments;
+    const int begin = seg * len, end = min(vocab, begin + len);
+    float best = -INFINITY;
+    int best_id = 0;
+    if (begin < end) {
+        block_argmax(logits + (size_t)row * vocab + begin, end - begin, best, best_id, sv, si);
+        best_id = best == -INFINITY ? 0x7fffffff : best_id + begin;
+    } else {
+        best_id = 0x7fffffff;
+    }
+    if (threadIdx.x == 0) {
+        seg_value[row * kArgmaxSegments + seg] = best;
+        seg_index[row * kArgmaxSegments + seg] = best_id;
+    }
+}
+
+__global__ void __launch_bounds__(kArgmaxSegments)
+argmax_pick_kernel(const float* __restrict__ seg_value, const int* __restrict__ seg_index, int32_t* __restrict__ tokens) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    float v = seg_value[row * kArgmaxSegments + threadIdx.x];
+    int id = seg_index[row * kArgmaxSegments + threadIdx.x];
+    if (v == -INFINITY) id = 0x7fffffff;
+    __shared__ float sv[2];
+    __shared__ int si[2];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, id, o);
+        better(v, id, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = id; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        better(v, id, sv[1], si[1]);
+        tokens[row] = id == 0x7fffffff ? 0 : id;
+    }
+}
+
 // p = softmax(logits / temperature) over finite entries; the token is the first index whose
 // inclusive CDF, accumulated in index order, exceeds u.  The vocabulary is cut into 32
 // contiguous segments, one per warp; segment sums locate the segment, then one warp walks it
@@ -134,6 +185,22 @@ extern "C" int citlali_argmax_rows(const float* logits, int32_t* tokens, int row
         return kBadShape;
     }
     launch_kernel(argmax_rows_kernel, rows, 1024, 0, stream, logits, tokens, vocab);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+// The same with `scratch` (rows * 128 floats, 4-byte aligned): the vocabulary of every row is
+// scanned by 64 blocks.  Worth it from a few thousand entries on.
+extern "C" int citlali_argmax_rows_wide(const float* logits, int32_t* tokens, float* scratch, int rows, int vocab,
+                                        cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || rows > 65535 || scratch == nullptr) {
+        set_last_error("argmax_rows_wide: vocabulary %d must be positive, rows %d at most 65535, scratch given", vocab, rows);
+        return kBadShape;
+    }
+    float* seg_value = scratch;
+    int* seg_index = reinterpret_cast<int*>(scratch + (size_t)rows * kArgmaxSegments);
+    launch_kernel(argmax_segments_kernel, dim3(kArgmaxSegments, rows), 256, 0, stream, logits, seg_value, seg_index, vocab);
+    launch_kernel(argmax_pick_kernel, rows, kArgmaxSegments, 0, stream, (const float*)seg_value, (const int*)seg_index, tokens);
     return CITLALI_LAUNCH_CHECK();
 }
 

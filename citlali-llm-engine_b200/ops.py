@@ -47,7 +47,7 @@ def _stream():
 
 
 _launches = 0
-_KERNELS_PER_CALL = {"attention_decode": 2}
+_KERNELS_PER_CALL = {"attention_decode": 2, "argmax_rows_wide": 2}
 
 
 def launch_count() -> int:
@@ -154,6 +154,11 @@ def argmax_rows(logits: torch.Tensor, tokens: torch.Tensor):
     _need_cuda(logits, tokens)
     require(logits.dtype == torch.float32 and tokens.dtype == torch.int32, "argmax_rows: float32 in, int32 out")
     rows, vocab = logits.shape
+    if vocab >= 8192:
+        scratch = _scratch(logits.device, "argmax segments", rows * 128 * 4)
+        _check(lib().citlali_argmax_rows_wide(_ptr(logits), _ptr(tokens), _ptr(scratch), _i(rows), _i(vocab), _stream()),
+               "argmax_rows_wide")
+        return
     _check(lib().citlali_argmax_rows(_ptr(logits), _ptr(tokens), _i(rows), _i(vocab), _stream()), "argmax_rows")
 
 

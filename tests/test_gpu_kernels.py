@@ -253,10 +253,14 @@ def test_argmax_rows_rules():
     tok = torch.zeros(6, dtype=torch.int32, device=DEV)
     ops.argmax_rows(logits.to(DEV), tok)
     assert tok.tolist() == [plain.greedy(r) for r in logits] and tok.tolist()[:5] == [17, 0, 999, 0, 0]
-    big = torch.randn(3, 151936)
-    tok = torch.zeros(3, dtype=torch.int32, device=DEV)
+    big = torch.randn(5, 151936)                                        # wide rows are scanned by 64 blocks each
+    big[1, :] = 3.0                                                      # all equal: index 0
+    big[2, 100000] = 50.0; big[2, 5] = 50.0                              # a tie across segments: the lowest index
+    big[3, :] = float("nan")                                             # nothing finite: id 0
+    big[4, 151935] = 60.0; big[4, 77] = float("inf")
+    tok = torch.zeros(5, dtype=torch.int32, device=DEV)
     ops.argmax_rows(big.to(DEV), tok)
-    assert tok.tolist() == big.argmax(dim=1).tolist()
+    assert tok.tolist() == [int(big[0].argmax()), 0, 5, 0, 151935]
 
 
 @pytest.mark.parametrize("V", [7, 1000, 4097, 151936])
