@@ -17,70 +17,94 @@ constexpr int kMaxPairsPerLane = 4;   // head_dim <= 256: 128 rotation pairs ove
 //         theta^(-2i/d) is tabulated by the host).  No rounding between the two.
 //   k, v: stored at the row's position in the slot's pages (store_kv_kernel,
 //         kernels.cu:524-533), k after norm and rotation, v as projected.
+constexpr int kRopeWarps = 8;      // warps per block
+constexpr int kRopeBatch = 4;      // heads a warp has in flight
+
 template <typename T, typename TG>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRopeWarps * 32)
 qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
                           const float* __restrict__ inv_freq,
                           const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                           const int32_t* __restrict__ page_table, int page_table_stride,
                           T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
-                          int nq, int nkv, int d, float eps, int write_cache) {
+                          int nq, int nkv, int d, float eps, int write_cache, int heads_per_block) {
+    extern __shared__ float2 cos_sin[];                 // [d / 2]: the row's rotation, shared by the block's heads
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
-    const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int total = nq + 2 * nkv;
-    if (head >= total) return;
+    const int head_begin = blockIdx.y * heads_per_block;
+    const int head_end = min(total, head_begin + heads_per_block);
     const int half = d >> 1;
-    T* src = qkv + ((size_t)row * total + head) * d;
     const int pos = row_pos[row];
-
-    size_t cache_off = 0;
-    if (head >= nq && write_cache) {
-        const int g = (head - nq) % nkv;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        cos_sin[i] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    size_t page_off = 0;
+    if (write_cache) {
         const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
-        cache_off = (((size_t)page * nkv + g) * page_size + (pos % page_size)) * d;
+        page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * d;       // + kv head * page_size * d
     }
+    T* row_ptr = qkv + (size_t)row * total * d;
 
-    if (head >= nq + nkv) {   // a value head: a copy into the cache
-        if (!write_cache) return;
-        for (int i = lane; i < d; i += 32) v_pool[cache_off + i] = src[i];
-        return;
-    }
-
-    const TG* gain = head < nq ? q_gain : k_gain;
-    float x0[kMaxPairsPerLane], x1[kMaxPairsPerLane];
-    float ss = 0.0f;
+    // a warp takes heads warp, warp + 8, ...; it loads kRopeBatch of them before it works on any
+    for (int h0 = head_begin + warp; h0 < head_end; h0 += kRopeWarps * kRopeBatch) {
+        float x0[kRopeBatch][kMaxPairsPerLane], x1[kRopeBatch][kMaxPairsPerLane];
 #pragma unroll
-    for (int j = 0; j < kMaxPairsPerLane; ++j) {
-        const int i = lane + 32 * j;
-        x0[j] = x1[j] = 0.0f;
-        if (i < half) {
-            x0[j] = ldf(src, i);
-            x1[j] = ldf(src, i + half);
-            ss = fmaf(x0[j], x0[j], ss);
-            ss = fmaf(x1[j], x1[j], ss);
-        }
-    }
-    ss = warp_sum(ss);
-    const float inv = gain ? rsqrtf(ss / (float)d + eps) : 1.0f;
-    T* dst = head < nq ? src : (k_pool + cache_off);
-    const bool store = head < nq || write_cache;
+        for (int b = 0; b < kRopeBatch; ++b) {
+            const int head = h0 + b * kRopeWarps;
 #pragma unroll
-    for (int j = 0; j < kMaxPairsPerLane; ++j) {
-        const int i = lane + 32 * j;
-        if (i < half) {
-            float a = x0[j], b = x1[j];
-            if (gain) {
-                a = a * inv * ldf(gain, i);
-                b = b * inv * ldf(gain, i + half);
+            for (int j = 0; j < kMaxPairsPerLane; ++j) {
+                const int i = lane + 32 * j;
+                const bool on = head < head_end && i < half;
+                x0[b][j] = on ? ldf(row_ptr, (size_t)head * d + i) : 0.0f;
+                x1[b][j] = on ? ldf(row_ptr, (size_t)head * d + i + half) : 0.0f;
             }
-            float s, c;
-            sincosf((float)pos * inv_freq[i], &s, &c);
-            if (store) {
-                stf(dst, i, a * c - b * s);
-                stf(dst, i + half, a * s + b * c);
+        }
+#pragma unroll
+        for (int b = 0; b < kRopeBatch; ++b) {
+            const int head = h0 + b * kRopeWarps;
+            if (head >= head_end) break;
+            if (head >= nq + nkv) {                     // a value head goes to the cache as it is
+                if (write_cache) {
+                    T* dst = v_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+#pragma unroll
+                    for (int j = 0; j < kMaxPairsPerLane; ++j) {
+                        const int i = lane + 32 * j;
+                        if (i < half) { stf(dst, i, x0[b][j]); stf(dst, i + half, x1[b][j]); }
+                    }
+                }
+                continue;
+            }
+            const bool is_q = head < nq;
+            const TG* gain = is_q ? q_gain : k_gain;
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kMaxPairsPerLane; ++j) {
+                ss = fmaf(x0[b][j], x0[b][j], ss);
+                ss = fmaf(x1[b][j], x1[b][j], ss);
+            }
+            ss = warp_sum(ss);
+            const float inv = gain ? rsqrtf(ss / (float)d + eps) : 1.0f;
+            if (!is_q && !write_cache) continue;
+            T* dst = is_q ? row_ptr + (size_t)head * d : k_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+#pragma unroll
+            for (int j = 0; j < kMaxPairsPerLane; ++j) {
+                const int i = lane + 32 * j;
+                if (i < half) {
+                    float a = x0[b][j], c2 = x1[b][j];
+                    if (gain) {
+                        a = a * inv * ldf(gain, i);
+                        c2 = c2 * inv * ldf(gain, i + half);
+                    }
+                    const float c = cos_sin[i].x, sn = cos_sin[i].y;
+                    stf(dst, i, a * c - c2 * sn);
+                    stf(dst, i + half, a * sn + c2 * c);
+                }
             }
         }
     }
@@ -181,16 +205,19 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
         return kBadShape;
     }
     const int total = nq + 2 * nkv;
-    dim3 grid(rows, (total + 3) / 4);
+    // many rows (prompts): one block rotates all heads of a row from one table; few rows (decoding):
+    // eight heads a block, so that there are enough blocks
+    const int heads_per_block = rows >= 128 ? total : kRopeWarps;
+    dim3 grid(rows, (total + heads_per_block - 1) / heads_per_block);
     if (grid.y > 65535) {
         set_last_error("qk_norm_rope_cache: too many heads (%d)", total);
         return kTooLarge;
     }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
-            launch_kernel(qk_norm_rope_cache_kernel<T, TG>, grid, 128, 0, stream, 
+            launch_kernel(qk_norm_rope_cache_kernel<T, TG>, grid, kRopeWarps * 32, (size_t)(head_dim / 2) * sizeof(float2), stream, 
                 (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, row_slot, row_pos, page_table,
-                page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache);
+                page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache, heads_per_block);
             return CITLALI_LAUNCH_CHECK();
         });
     });

@@ -130,13 +130,21 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         // mask, then the running maximum of each row (shared by the four lanes of a row)
         const int key_base = tile * kTileK + (lane & 3) * 2;
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        // only tiles that reach past the warp's first row, or start before its last row's window, need the mask
+        const int warp_pos = past + q0 + warp * 16;
+        const bool masked = tile * kTileK + kTileK - 1 > warp_pos || (window > 0 && tile * kTileK < warp_pos + 15 - window + 1);
+        if (masked) {
+#pragma unroll
+            for (int i = 0; i < kTileK / 8; ++i) {
+                const int key = key_base + i * 8;
+                if (key > pos0 || key < lo0) s[i][0] = -INFINITY;
+                if (key + 1 > pos0 || key + 1 < lo0) s[i][1] = -INFINITY;
+                if (key > pos1 || key < lo1) s[i][2] = -INFINITY;
+                if (key + 1 > pos1 || key + 1 < lo1) s[i][3] = -INFINITY;
+            }
+        }
 #pragma unroll
         for (int i = 0; i < kTileK / 8; ++i) {
-            const int key = key_base + i * 8;
-            if (key > pos0 || key < lo0) s[i][0] = -INFINITY;
-            if (key + 1 > pos0 || key + 1 < lo0) s[i][1] = -INFINITY;
-            if (key > pos1 || key < lo1) s[i][2] = -INFINITY;
-            if (key + 1 > pos1 || key + 1 < lo1) s[i][3] = -INFINITY;
             mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
             mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
         }
@@ -145,13 +153,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         // a row that has seen no key yet keeps maximum -inf; use 0 in its exponents so nothing is NaN
         const float ref0 = mn0 == -INFINITY ? 0.0f : mn0 * scale_log2, ref1 = mn1 == -INFINITY ? 0.0f : mn1 * scale_log2;
-        const float a0 = exp2f(m0 * scale_log2 - ref0), a1 = exp2f(m1 * scale_log2 - ref1);
+        const float a0 = fast_exp2(m0 * scale_log2 - ref0), a1 = fast_exp2(m1 * scale_log2 - ref1);
         m0 = mn0; m1 = mn1;
         float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
         for (int i = 0; i < kTileK / 8; ++i) {
-            s[i][0] = exp2f(s[i][0] * scale_log2 - ref0); s[i][1] = exp2f(s[i][1] * scale_log2 - ref0);
-            s[i][2] = exp2f(s[i][2] * scale_log2 - ref1); s[i][3] = exp2f(s[i][3] * scale_log2 - ref1);
+            s[i][0] = fast_exp2(s[i][0] * scale_log2 - ref0); s[i][1] = fast_exp2(s[i][1] * scale_log2 - ref0);
+            s[i][2] = fast_exp2(s[i][2] * scale_log2 - ref1); s[i][3] = fast_exp2(s[i][3] * scale_log2 - ref1);
             sum0 += s[i][0] + s[i][1];
             sum1 += s[i][2] + s[i][3];
         }

@@ -58,6 +58,47 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const TG* __restric
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) stf(dst, i, src[i] * inv * ldf(gain, i));
 }
 
+// The same for rows of at most 8192 elements that are a multiple of 4: every thread keeps its
+// part of the row in registers, so the row is read once, with 16-byte loads.
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+rms_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
+                     const int32_t* __restrict__ row_index, TO* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * hidden);
+    const int quads = hidden >> 2;
+    float4 v[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int q = threadIdx.x + j * 256;
+        v[j] = q < quads ? src[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    TO* dst = out + (size_t)row * hidden;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int q = threadIdx.x + j * 256;
+        if (q < quads) {
+            const int i = q * 4;
+            const float a = v[j].x * inv * ldf(gain, i), b = v[j].y * inv * ldf(gain, i + 1);
+            const float c = v[j].z * inv * ldf(gain, i + 2), d = v[j].w * inv * ldf(gain, i + 3);
+            if constexpr (sizeof(TO) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                *reinterpret_cast<uint2*>(dst + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+                *reinterpret_cast<float4*>(dst + i) = make_float4(a, b, c, d);
+            }
+        }
+    }
+}
+
 // act = g / (1 + exp(-g)) * u (reference: swiglu_kernel, kernels.cu:474-482).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ act, int inter, int run) {
@@ -97,7 +138,10 @@ extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
         return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-            launch_kernel(rms_norm_kernel<TG, TO>, rows, threads, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
+            if (hidden % 4 == 0 && hidden <= 8192)
+                launch_kernel(rms_norm_rows_kernel<TG, TO>, rows, 256, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
+            else
+                launch_kernel(rms_norm_kernel<TG, TO>, rows, threads, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
             return CITLALI_LAUNCH_CHECK();
         });
     });

@@ -55,7 +55,7 @@ struct GemmParams {
 template <int BN>
 constexpr int stages_for(bool swapped) {
     // swapped (decoding): two blocks per SM, about 100 KB each; normal: one block of 192 KB
-    return swapped ? (BN <= 16 ? 6 : BN <= 32 ? 5 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : 4);
+    return swapped ? (BN <= 16 ? 6 : BN <= 32 ? 5 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
 }
 
 template <int BN, bool kSwapped>
@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(kThreads, (kSwapped && BN <= 64) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int kStages = stages_for<BN>(kSwapped);
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
-    constexpr uint32_t kTmemCols = (kAccStages * BN) < 32 ? 32 : (kAccStages * BN);
+    constexpr uint32_t kTmemCols = (kAccStages * BN) <= 32 ? 32 : (kAccStages * BN) <= 64 ? 64 : (kAccStages * BN) <= 128 ? 128
+                                   : (kAccStages * BN) <= 256 ? 256 : 512;        // a power of two
     constexpr uint32_t kIdesc = instr_desc_bf16(kBM, BN);
 
     extern __shared__ uint8_t smem_raw[];
@@ -484,8 +485,20 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
         if (s < 1) s = 1;
         pl.splits = s;
     } else {
-        pl.bn = N >= 256 ? 256 : 128;
+        // The grid runs in waves of one block per SM; the narrow tile's width is chosen so that the last
+        // wave is as full as possible.  Measured at 2,048 rows, a tile's time hardly depends on its width
+        // (operand traffic from L2 bounds it, not the MMAs): about 20 + 0.03 x width microseconds at K = 4096.
+        pl.bn = 128;
         pl.splits = 1;
+        if (N >= 192) {
+            const int tiles_m = (M + kBM - 1) / kBM;
+            long best = -1;
+            for (int bn : {256, 240, 224, 208, 192}) {
+                const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+                const long cost = ((tiles + sm_count - 1) / sm_count) * (2000 + 3 * bn);
+                if (best < 0 || cost < best) { best = cost; pl.bn = bn; }
+            }
+        }
     }
     return pl;
 }
@@ -610,8 +623,14 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
     } else {
         if ((rc = make_map(&ma, x, M, K, kBM))) return rc;
         if ((rc = make_map(&mb, w, N, K, pl.bn))) return rc;
-        if (pl.bn == 256) rc = launch<256, false>(ma, mb, p, sm_count, stream);
-        else rc = launch<128, false>(ma, mb, p, sm_count, stream);
+        switch (pl.bn) {
+            case 256: rc = launch<256, false>(ma, mb, p, sm_count, stream); break;
+            case 240: rc = launch<240, false>(ma, mb, p, sm_count, stream); break;
+            case 224: rc = launch<224, false>(ma, mb, p, sm_count, stream); break;
+            case 208: rc = launch<208, false>(ma, mb, p, sm_count, stream); break;
+            case 192: rc = launch<192, false>(ma, mb, p, sm_count, stream); break;
+            default: rc = launch<128, false>(ma, mb, p, sm_count, stream); break;
+        }
     }
     return rc;
 }
