@@ -14,7 +14,7 @@ from helpers import TINY, random_tokens
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 11, 17, 40, 70, 128, 1, 33], "B": [1, 7, 23, 40, 150, 256, 64, 65],
-           "C": [33, 64, 65, 300, 129, 2, 97]}
+           "C": [33, 64, 65, 300, 129, 2, 97], "D": [700, 129, 65, 260, 31]}
 
 # float32: the engine and the exact (float64) evaluation of the same formulas differ by 32-bit
 # rounding only.  bfloat16: activations are rounded to 8 significant bits at each store.
@@ -55,7 +55,7 @@ def check(got, want_rows, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_tail_and_batched_agree_with_plain(model_dirs, name, dtype):
     stored = "float32" if dtype == "float32" else "bfloat16"
     want = plain_rows(model_dirs, name, stored)
