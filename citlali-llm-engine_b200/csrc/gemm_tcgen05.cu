@@ -58,6 +58,93 @@ constexpr int stages_for(bool swapped) {
     return swapped ? (BN <= 16 ? 6 : BN <= 32 ? 5 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
 }
 
+// The block that brought a tile's last split-K partial adds all of them and writes the tile.  Only
+// the swapped form splits K: the tile's 128 rows are output features n, its BN columns are rows m of
+// x, and partials lie [split][m][n] with n contiguous.  An item is four consecutive n of one m; the
+// 128 epilogue threads share the tile's BN * 32 items, kItems at a time so that many loads are in
+// flight; every sum runs in split order.
+template <int BN, int kItems, bool kGate>
+__device__ __forceinline__ void finish_split_tile(const GemmParams& p, const float* __restrict__ part, size_t tile_elems,
+                                                  int n_tile, int m_tile, int et) {
+    float* outf = (float*)p.out;
+    __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
+    const int half_n = p.N >> 1;
+#pragma unroll 1
+    for (int item0 = et; item0 < BN * 32; item0 += 128 * kItems) {
+        float4 a[kItems], u[kItems];
+        const float* src[kItems];
+        bool on[kItems];
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            const int item = item0 + 128 * k;
+            const int c = item >> 5, l4 = item & 31;
+            on[k] = item < BN * 32 && m_tile + c < p.M && n_tile + 4 * l4 < p.N && !(kGate && (l4 & 4));
+            src[k] = part + (size_t)c * kBM + 4 * l4;
+            a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            u[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll 1
+        for (int z0 = 0; z0 < p.splits; z0 += 4) {
+            float4 t[kItems][4], tu[kGate ? kItems : 1][4];
+#pragma unroll
+            for (int k = 0; k < kItems; ++k)
+#pragma unroll
+                for (int z = 0; z < 4; ++z) {
+                    const bool live = on[k] && z0 + z < p.splits;
+                    t[k][z] = live ? __ldcg(reinterpret_cast<const float4*>(src[k] + (size_t)(z0 + z) * tile_elems))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (kGate)
+                        tu[k][z] = live ? __ldcg(reinterpret_cast<const float4*>(src[k] + (size_t)(z0 + z) * tile_elems + 16))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+            for (int k = 0; k < kItems; ++k)
+#pragma unroll
+                for (int z = 0; z < 4; ++z) {
+                    a[k].x += t[k][z].x; a[k].y += t[k][z].y; a[k].z += t[k][z].z; a[k].w += t[k][z].w;
+                    if (kGate) { u[k].x += tu[k][z].x; u[k].y += tu[k][z].y; u[k].z += tu[k][z].z; u[k].w += tu[k][z].w; }
+                }
+        }
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+            if (!on[k]) continue;
+            const int item = item0 + 128 * k;
+            const int m = m_tile + (item >> 5), n0 = n_tile + 4 * (item & 31);
+            const float v[4] = {a[k].x, a[k].y, a[k].z, a[k].w};
+            if (kGate) {
+                const float uu[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+                const size_t o = (size_t)m * half_n + (n0 >> 5) * 16 + (n0 & 15);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (n0 + e < p.N) outh[o + e] = __float2bfloat16_rn(silu_mul(v[e], uu[e]));
+                continue;
+            }
+            const size_t o = (size_t)m * p.N + n0;
+            if (n0 + 4 <= p.N && (p.N & 3) == 0) {
+                if (p.out_kind == kStoreBF16) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                    *reinterpret_cast<uint2*>(outh + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                } else {
+                    float4 w = a[k];
+                    if (p.out_kind == kAddF32) {
+                        const float4 old = *reinterpret_cast<const float4*>(outf + o);
+                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                    }
+                    *reinterpret_cast<float4*>(outf + o) = w;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (n0 + e < p.N) {
+                        if (p.out_kind == kStoreBF16) outh[o + e] = __float2bfloat16_rn(v[e]);
+                        else if (p.out_kind == kAddF32) outf[o + e] += v[e];
+                        else outf[o + e] = v[e];
+                    }
+            }
+        }
+    }
+}
+
 template <int BN, bool kSwapped>
 __global__ void __launch_bounds__(kThreads, (kSwapped && BN <= 64) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -339,72 +426,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (last_flag) {
                     __threadfence();
-                    // Only the swapped form splits K: the tile's 128 rows are output features n, its BN
-                    // columns are rows m of x, and partials lie [split][m][n] with n contiguous.  An item is
-                    // four consecutive n of one m; the 128 epilogue threads share the tile's BN * 32 items.
                     const int et = threadIdx.x - 64;
-                    const int n_tile = ta * kBM, m_tile = tb * BN;
-                    const int half_n = p.N >> 1;
-                    const bool gate = p.out_kind == kSwigluBF16;
-#pragma unroll 1
-                    for (int item = et; item < BN * 32; item += 128) {
-                        const int c = item >> 5, l4 = item & 31;
-                        const int m = m_tile + c, n0 = n_tile + 4 * l4;
-                        if (m >= p.M || n0 >= p.N) continue;
-                        if (gate && (l4 & 4)) continue;                 // an up run: done with its gate run
-                        const float* src = part + (size_t)c * kBM + 4 * l4;
-                        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), u = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-                        for (int z0 = 0; z0 < p.splits; z0 += 8) {
-                            float4 t[8], tu[8];
-#pragma unroll
-                            for (int z = 0; z < 8; ++z) {
-                                const bool on = z0 + z < p.splits;
-                                t[z] = on ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z0 + z) * tile_elems))
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (gate)
-                                    tu[z] = on ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z0 + z) * tile_elems + 16))
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-#pragma unroll
-                            for (int z = 0; z < 8; ++z) {
-                                a.x += t[z].x; a.y += t[z].y; a.z += t[z].z; a.w += t[z].w;
-                                if (gate) { u.x += tu[z].x; u.y += tu[z].y; u.z += tu[z].z; u.w += tu[z].w; }
-                            }
-                        }
-                        const float v[4] = {a.x, a.y, a.z, a.w};
-                        if (gate) {
-                            const float uu[4] = {u.x, u.y, u.z, u.w};
-                            const size_t o = (size_t)m * half_n + (n0 >> 5) * 16 + (n0 & 15);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                if (n0 + k < p.N) outh[o + k] = __float2bfloat16_rn(silu_mul(v[k], uu[k]));
-                        } else {
-                            const size_t o = (size_t)m * p.N + n0;
-                            if (n0 + 4 <= p.N && (p.N & 3) == 0) {
-                                if (p.out_kind == kStoreBF16) {
-                                    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-                                    *reinterpret_cast<uint2*>(outh + o) =
-                                        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                                } else {
-                                    float4 w = a;
-                                    if (p.out_kind == kAddF32) {
-                                        const float4 old = *reinterpret_cast<const float4*>(outf + o);
-                                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
-                                    }
-                                    *reinterpret_cast<float4*>(outf + o) = w;
-                                }
-                            } else {
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    if (n0 + k < p.N) {
-                                        if (p.out_kind == kStoreBF16) outh[o + k] = __float2bfloat16_rn(v[k]);
-                                        else if (p.out_kind == kAddF32) outf[o + k] += v[k];
-                                        else outf[o + k] = v[k];
-                                    }
-                            }
-                        }
-                    }
+                    if (p.out_kind == kSwigluBF16) finish_split_tile<BN, 2, true>(p, part, tile_elems, ta * kBM, tb * BN, et);
+                    else finish_split_tile<BN, 4, false>(p, part, tile_elems, ta * kBM, tb * BN, et);
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is read by all before it is rewritten
             }
