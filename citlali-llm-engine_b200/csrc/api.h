@@ -75,6 +75,17 @@ int citlali_attention_prefill(const void* q, int q_stride, const void* k_pool, c
                               int nq, int nkv, int head_dim, int page_size, int window, float scale,
                               cudaStream_t stream);
 
+// The same on tcgen05 (scores and output in tensor memory), for head size 128 and pages of 64.
+// total_rows: rows of q over all sequences; pool_pages: pages of the layer's key and value pools.
+int citlali_attention_prefill_tc_supports(int head_dim, int page_size);
+int citlali_attention_prefill_tc(const void* q, int q_stride, int total_rows,
+                                 const void* k_pool, const void* v_pool, int pool_pages,
+                                 const int32_t* page_table, int page_table_stride,
+                                 const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_past,
+                                 void* out, int out_stride, int sequences, int max_new,
+                                 int nq, int nkv, int head_dim, int page_size, int window, float scale,
+                                 int32_t* error_flag, cudaStream_t stream);
+
 // tokens[r] = argmax of logits[r, :] over finite values, lowest index on ties.
 int citlali_argmax_rows(const float* logits, int32_t* tokens, int rows, int vocab, cudaStream_t stream);
 // The same with 64 blocks per row; scratch holds rows * 128 floats.

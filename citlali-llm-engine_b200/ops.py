@@ -185,6 +185,12 @@ def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, sc
                          batch.row_pos, out, nq, nkv, head_dim, cache_view.page_size, window,
                          cache_view.page_table.shape[1] * cache_view.page_size, scale)
         return
+    if (q.dtype == torch.bfloat16 and q_stride % 8 == 0 and out.shape[1] % 8 == 0 and batch.max_new >= 48
+            and lib().citlali_attention_prefill_tc_supports(_i(head_dim), _i(cache_view.page_size))):
+        attention_prefill_tc(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table, batch.seq_start,
+                             batch.seq_slot, batch.seq_past, out, batch.sequences, batch.max_new, nq, nkv, head_dim,
+                             cache_view.page_size, window, scale)
+        return
     if (q.dtype == torch.bfloat16 and q_stride % 8 == 0
             and lib().citlali_attention_prefill_supports(_i(head_dim), _i(cache_view.page_size))):
         attention_prefill(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table, batch.seq_start,
@@ -205,6 +211,19 @@ def attention_prefill(q, q_stride, k_pool, v_pool, page_table, seq_start, seq_sl
         _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(seq_start), _ptr(seq_slot), _ptr(seq_past), _ptr(out), _i(out.shape[1]), _i(sequences), _i(max_new),
         _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _f(scale), _stream()), "attention_prefill")
+
+
+def attention_prefill_tc(q, q_stride, k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out, sequences, max_new,
+                         nq, nkv, head_dim, page_size, window, scale, error_flag=None):
+    """Prompt attention on tcgen05 (head size 128, pages of 64)."""
+    _need_cuda(k_pool, v_pool, page_table, seq_start, seq_slot, seq_past, out, error_flag)
+    require(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+            "attention_prefill_tc: bfloat16 only")
+    _check(lib().citlali_attention_prefill_tc(
+        _ptr(q), _i(q_stride), _i(q.shape[0]), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(page_table),
+        _i(page_table.shape[1]), _ptr(seq_start), _ptr(seq_slot), _ptr(seq_past), _ptr(out), _i(out.shape[1]),
+        _i(sequences), _i(max_new), _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _f(scale),
+        _ptr(error_flag), _stream()), "attention_prefill_tc")
 
 
 def attention_decode(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos, out, nq, nkv, head_dim,
