@@ -47,9 +47,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
     dependents_may_launch();
     wait_for_predecessor();
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // blocks are handed out x fastest: all heads of the last query tile (it sees the most keys) first
+    const int seq = blockIdx.z, head = blockIdx.x;
     const int row0 = seq_start[seq], n_new = seq_start[seq + 1] - row0;
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * kTileQ;      // long rows first: they see the most keys
+    const int q0 = (gridDim.y - 1 - blockIdx.y) * kTileQ;
     if (q0 >= n_new) return;
     const int past = seq_past[seq];
     const int g = head / (nq / nkv);
@@ -214,7 +215,7 @@ static int launch(const void* q, int q_stride, const void* k_pool, const void* v
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((max_new + kTileQ - 1) / kTileQ, nq, sequences);
+    dim3 grid(nq, (max_new + kTileQ - 1) / kTileQ, sequences);
     launch_kernel(kernel, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
                                                  (const __nv_bfloat16*)v_pool, page_table, page_table_stride, seq_start,
                                                  seq_slot, seq_past, (__nv_bfloat16*)out, out_stride, nq, nkv, window,
@@ -252,7 +253,7 @@ extern "C" int citlali_attention_prefill(const void* q, int q_stride, const void
                        "and 256, pages of 64)", head_dim, page_size);
         return kBadShape;
     }
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq > 65535 || sequences > 65535) {
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || max_new / fa::kTileQ >= 65535 || sequences > 65535) {
         set_last_error("attention_prefill: bad head counts (%d over %d) or too many sequences (%d)", nq, nkv, sequences);
         return kBadShape;
     }
