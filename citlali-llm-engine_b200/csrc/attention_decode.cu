@@ -477,7 +477,7 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         const int max_pages = (max_positions + page_size - 1) / page_size;
         chunk_pages = 16;
         for (int c = 2; c <= 16; c *= 2)
-            if ((long long)rows * kv_tiles * ((max_pages + c - 1) / c) <= 600) { chunk_pages = c; break; }
+            if ((long long)rows * kv_tiles * ((max_pages + c - 1) / c) <= 300) { chunk_pages = c; break; }
     }
     const int chunk_keys = chunk_pages * page_size;
     const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;

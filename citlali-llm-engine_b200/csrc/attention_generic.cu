@@ -18,7 +18,7 @@ constexpr int kMaxPairsPerLane = 4;   // head_dim <= 256: 128 rotation pairs ove
 //   k, v: stored at the row's position in the slot's pages (store_kv_kernel,
 //         kernels.cu:524-533), k after norm and rotation, v as projected.
 constexpr int kRopeWarps = 8;      // warps per block
-constexpr int kRopeBatch = 4;      // heads a warp has in flight
+constexpr int kRopeBatch = 1;      // heads a warp has in flight (more than one was measured slower)
 
 template <typename T, typename TG>
 __global__ void __launch_bounds__(kRopeWarps * 32)
