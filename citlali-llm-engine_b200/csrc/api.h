@@ -99,17 +99,15 @@ int citlali_sample_rows(const float* logits, const float* temperature, const flo
 
 // The tensor-core product (bfloat16 operands, float accumulation).  citlali_gemm_tc_plan tells
 // how a shape runs: whether the weights are the 128-row operand (*swapped), the narrow tile
-// (*bn), the K split (*splits), the bytes of scratch for split-K partials and the number of
-// tile counters (ints that are zero between launches).  force_splits > 0 replaces the plan's split.
-int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits,
-                         size_t* workspace_bytes, int* tile_counters);
+// (*bn) and the K split (*splits).  force_splits > 0 replaces the plan's split (at most 8).
+int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits);
 // y = x[M, K] . w[N, K]^T.  mode bits: 1 = y (float32) += product; 2 = SiLU-gate epilogue (w's rows
 // alternate in runs of 16 between gate and up; y is bfloat16 [M, N/2]).  K must be a multiple of 8
-// and the operands 16-byte aligned.  A shape that splits K sums its partials inside the kernel, in
-// split order.  error_flag[1..2] receive the code and block of a wait that ran out.
+// and the operands 16-byte aligned.  A shape that splits K runs each tile's splits as a cluster
+// that sums its partials through distributed shared memory, in split order; no scratch is needed.
+// error_flag[1..2] receive the code and block of a wait that ran out.
 int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
-                    int mode, int force_splits, void* workspace, size_t workspace_bytes, int* tile_counters,
-                    int counters_len, int32_t* error_flag, int sm_count, cudaStream_t stream);
+                    int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -54,6 +54,34 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);     // errors surface in cudaGetLastError
 }
 
+// The same with the grid cut into clusters of `cluster_x` consecutive blocks (1: no clusters).
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                                    cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (dependent_launch_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float ldf(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ void stf(float* p, size_t i, float v) { p[i] = v; }

@@ -35,7 +35,7 @@ namespace tc {
 
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
 constexpr int kThreads = 192;
-constexpr int kMaxSplits = 16;
+constexpr int kMaxSplits = 8;       // a cluster's portable size
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
 
@@ -47,8 +47,6 @@ struct GemmParams {
     int M, N, K;           // the product's logical shape: y[M, N] = x[M, K] w[N, K]^T
     int rows_a, rows_b;    // rows of the 128-row operand and of the BN-row operand
     int splits;            // K is cut into this many ranges of whole 64-blocks
-    float* partials;       // split K: [tiles][splits][BN][128] float32
-    int* tile_counters;    // split K: one arrival counter per output tile, zero between launches
     int32_t* error_flag;
 };
 
@@ -58,28 +56,40 @@ constexpr int stages_for(bool swapped) {
     return swapped ? (BN <= 16 ? 6 : BN <= 32 ? 5 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
 }
 
-// The block that brought a tile's last split-K partial adds all of them and writes the tile.  Only
-// the swapped form splits K: the tile's 128 rows are output features n, its BN columns are rows m of
-// x, and partials lie [split][m][n] with n contiguous.  An item is four consecutive n of one m; the
-// 128 epilogue threads share the tile's BN * 32 items, kItems at a time so that many loads are in
-// flight; every sum runs in split order.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Four floats at shared-memory address `addr` of the block with rank `rank` in this cluster.
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
+// Split K: the blocks of a cluster hold one partial each of the same tile, [column][128 rows] floats at
+// shared-memory address `part_addr`.  Only the swapped form splits K: the tile's 128 rows are output
+// features n, its BN columns are rows m of x.  An item is four consecutive n of one m; the block with
+// rank r takes items r*128 .., (r + splits)*128 .., its 128 epilogue threads kItems of them at a time.
+// Every sum runs in rank (= split) order, whichever block computes it.
 template <int BN, int kItems, bool kGate>
-__device__ __forceinline__ void finish_split_tile(const GemmParams& p, const float* __restrict__ part, size_t tile_elems,
-                                                  int n_tile, int m_tile, int et) {
+__device__ __forceinline__ void finish_cluster_tile(const GemmParams& p, uint32_t part_addr, int n_tile, int m_tile, int rank, int et) {
     float* outf = (float*)p.out;
     __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
     const int half_n = p.N >> 1;
 #pragma unroll 1
-    for (int item0 = et; item0 < BN * 32; item0 += 128 * kItems) {
+    for (int item0 = rank * 128 + et; item0 < BN * 32; item0 += 128 * p.splits * kItems) {
         float4 a[kItems], u[kItems];
-        const float* src[kItems];
+        uint32_t src[kItems];
         bool on[kItems];
 #pragma unroll
         for (int k = 0; k < kItems; ++k) {
-            const int item = item0 + 128 * k;
+            const int item = item0 + 128 * p.splits * k;
             const int c = item >> 5, l4 = item & 31;
             on[k] = item < BN * 32 && m_tile + c < p.M && n_tile + 4 * l4 < p.N && !(kGate && (l4 & 4));
-            src[k] = part + (size_t)c * kBM + 4 * l4;
+            src[k] = part_addr + (uint32_t)(c * kBM + 4 * l4) * 4u;
             a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
             u[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -91,11 +101,8 @@ __device__ __forceinline__ void finish_split_tile(const GemmParams& p, const flo
 #pragma unroll
                 for (int z = 0; z < 4; ++z) {
                     const bool live = on[k] && z0 + z < p.splits;
-                    t[k][z] = live ? __ldcg(reinterpret_cast<const float4*>(src[k] + (size_t)(z0 + z) * tile_elems))
-                                   : make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (kGate)
-                        tu[k][z] = live ? __ldcg(reinterpret_cast<const float4*>(src[k] + (size_t)(z0 + z) * tile_elems + 16))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                    t[k][z] = live ? ld_cluster_f4(src[k], z0 + z) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (kGate) tu[k][z] = live ? ld_cluster_f4(src[k] + 64u, z0 + z) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
             for (int k = 0; k < kItems; ++k)
@@ -108,7 +115,7 @@ __device__ __forceinline__ void finish_split_tile(const GemmParams& p, const flo
 #pragma unroll
         for (int k = 0; k < kItems; ++k) {
             if (!on[k]) continue;
-            const int item = item0 + 128 * k;
+            const int item = item0 + 128 * p.splits * k;
             const int m = m_tile + (item >> 5), n0 = n_tile + 4 * (item & 31);
             const float v[4] = {a[k].x, a[k].y, a[k].z, a[k].w};
             if (kGate) {
@@ -158,7 +165,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full_bar[kAccStages], acc_empty_bar[kAccStages];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_word;
-    __shared__ int last_flag;
     volatile int* abort_flag = &abort_word;
 
     dependents_may_launch();
@@ -389,9 +395,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int i = ta * kBM + quarter * 32 + lane;     // row of the 128-row operand
             const bool empty_range = kb1 <= kb0;              // a split that got no K blocks contributes zeros
-            // split K: element (i, j) of split sp lives at partials[sp][i_local][j_local] of its tile, lanes contiguous
-            const size_t tile_elems = (size_t)kBM * BN;
-            float* part = p.partials + ((size_t)(tb * tiles_a + ta) * p.splits) * tile_elems;
+            // split K: this block's partial goes to its own shared memory, [column][128 rows], over the drained tile ring
+            float* part = reinterpret_cast<float*>(smem_raw + (tiles - raw));
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
@@ -401,9 +406,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int c = 0; c < 16; ++c) v[c] = empty_range ? 0.0f : __uint_as_float(r[c]);
                 if (p.splits > 1) {
-                    float* dst = part + (size_t)sp * tile_elems + (size_t)c0 * kBM + quarter * 32 + lane;
+                    float* dst = part + (size_t)c0 * kBM + quarter * 32 + lane;
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) __stcg(dst + (size_t)c * kBM, v[c]);
+                    for (int c = 0; c < 16; ++c) dst[(size_t)c * kBM] = v[c];
                 } else {
                     finish(v, i, tb * BN + c0, c0);
                 }
@@ -412,27 +417,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[as]));
-            if (p.splits > 1) {
-                // The block that brings a tile's last partial adds all of them, in split order, and
-                // finishes the tile.  Which block that is varies; the order of the sum does not.
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) {
-                    int* counter = p.tile_counters + (tb * tiles_a + ta);
-                    const int arrived = atomicAdd(counter, 1);
-                    last_flag = (arrived == p.splits - 1) ? 1 : 0;
-                    if (last_flag) *counter = 0;               // ready for the next launch
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (last_flag) {
-                    __threadfence();
-                    const int et = threadIdx.x - 64;
-                    if (p.out_kind == kSwigluBF16) finish_split_tile<BN, 2, true>(p, part, tile_elems, ta * kBM, tb * BN, et);
-                    else finish_split_tile<BN, 4, false>(p, part, tile_elems, ta * kBM, tb * BN, et);
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is read by all before it is rewritten
-            }
         }
+    }
+
+    if (p.splits > 1) {
+        // The `splits` blocks of a tile form a cluster (rank = split).  Each has its partial in shared memory;
+        // after a cluster barrier every block adds up a share of the tile, reading all partials through
+        // distributed shared memory in rank order, and writes that share.  A second barrier keeps every
+        // block's shared memory alive until all have read it.
+        __syncthreads();
+        cluster_sync_all();
+        if (warp >= 2) {
+            int ta, tb, sp;
+            decode(blockIdx.x, ta, tb, sp);
+            const uint32_t part_addr = tiles;
+            if (p.out_kind == kSwigluBF16) finish_cluster_tile<BN, 2, true>(p, part_addr, ta * kBM, tb * BN, sp, threadIdx.x - 64);
+            else finish_cluster_tile<BN, 2, false>(p, part_addr, ta * kBM, tb * BN, sp, threadIdx.x - 64);
+        }
+        cluster_sync_all();
     }
 
     tc_fence_before();
@@ -500,12 +502,14 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
         const int kblocks = (K + kBK - 1) / kBK;
         const int slots = sm_count * (pl.bn <= 64 ? 2 : 1);
         int s = slots / tiles;
-        // partials are written and read once each: keep them under a quarter of the weights' bytes
-        const int traffic_cap = K / (16 * pl.bn);
-        if (s > traffic_cap) s = traffic_cap;
-        if (force_splits > 0) s = force_splits;
         if (s > kblocks / 4) s = kblocks / 4;
         if (s > kMaxSplits) s = kMaxSplits;
+        // the splits of a tile are one cluster: sizes 2, 4, 8 are placed well, odd sizes were measured slower
+        int pow2 = 1;
+        while (pow2 * 2 <= s) pow2 *= 2;
+        s = pow2;
+        if (force_splits > 0) s = force_splits > kMaxSplits ? kMaxSplits : force_splits;
+        if (s > kblocks) s = kblocks;
         if (s < 1) s = 1;
         pl.splits = s;
     } else {
@@ -541,8 +545,9 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     const int tiles_a = (p.rows_a + kBM - 1) / kBM, tiles_b = (p.rows_b + BN - 1) / BN;
     const int units = tiles_a * tiles_b * p.splits;
     const int per_sm = (kSwapped && BN <= 64) ? 2 : 1;
-    const int grid = units < sm_count * per_sm ? units : sm_count * per_sm;
-    launch_kernel(kernel, grid, kThreads, smem, stream, ma, mb, p);
+    // split K: one block per (tile, split), the splits of a tile being one cluster; else a persistent grid
+    const int grid = p.splits > 1 ? units : (units < sm_count * per_sm ? units : sm_count * per_sm);
+    launch_kernel_clustered(kernel, grid, kThreads, smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -552,41 +557,25 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 using namespace citlali;
 using namespace citlali::tc;
 
-static size_t partial_bytes(const Plan& pl, int M, int N) {
-    if (pl.splits <= 1) return 0;
-    const int rows_a = pl.swapped ? N : M, rows_b = pl.swapped ? M : N;
-    const size_t tiles = (size_t)((rows_a + kBM - 1) / kBM) * ((rows_b + pl.bn - 1) / pl.bn);
-    return tiles * pl.splits * kBM * pl.bn * sizeof(float);
-}
-
-// How the product of this shape would run: *swapped, *bn, *splits, the bytes of float32 scratch
-// it needs for split-K partials (0 if it does not split) and the number of tile counters.
-extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits,
-                                    size_t* workspace_bytes, int* tile_counters) {
+// How the product of this shape would run: *swapped, *bn and the K split (*splits).
+extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits) {
     if (sm_count <= 0) sm_count = 148;
     Plan pl = make_plan(M, N, K, sm_count, force_splits);
     if (swapped) *swapped = pl.swapped;
     if (bn) *bn = pl.bn;
     if (splits) *splits = pl.splits;
-    if (workspace_bytes) *workspace_bytes = partial_bytes(pl, M, N);
-    if (tile_counters) {
-        const int rows_a = pl.swapped ? N : M, rows_b = pl.swapped ? M : N;
-        *tile_counters = pl.splits > 1 ? ((rows_a + kBM - 1) / kBM) * ((rows_b + pl.bn - 1) / pl.bn) : 0;
-    }
     return 0;
 }
 
 // y = x . w^T with x [M, K] and w [N, K] bfloat16, contiguous, 16-byte aligned, K a multiple of 8.
 // `mode` bits: 1 = y (float32 [M, N]) += product; 2 = SiLU-gate epilogue: w's rows alternate in runs
 // of 16 between gate and up rows and y is bfloat16 [M, N/2] = silu(gate) * up (N a multiple of 32).
-// Without them y is [M, N] of y_dtype (0 float32, 1 bfloat16).  When the shape splits K (see
-// citlali_gemm_tc_plan), `workspace` must hold the reported bytes and `tile_counters` the reported
-// number of ints, all zero: every block writes its partial there, and the block that brings a
-// tile's last partial adds them in split order and writes the tile; the counters are zero again
-// when the kernel ends.  `force_splits` > 0 replaces the plan's K split (for tuning and tests).
+// Without them y is [M, N] of y_dtype (0 float32, 1 bfloat16).  A shape that splits K (few rows, see
+// citlali_gemm_tc_plan) runs the splits of a tile as one thread-block cluster whose blocks add their
+// partial sums through distributed shared memory in split order; it needs no scratch memory.
+// `force_splits` > 0 replaces the plan's K split (for tuning and tests; at most 8).
 extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
-                               int mode, int force_splits, void* workspace, size_t workspace_bytes, int* tile_counters,
-                               int counters_len, int32_t* error_flag, int sm_count, cudaStream_t stream) {
+                               int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream) {
     const bool accumulate = (mode & 1) != 0, swiglu = (mode & 2) != 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) {
@@ -617,22 +606,8 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
     p.error_flag = error_flag;
     p.out = y;
     p.out_kind = swiglu ? kSwigluBF16 : accumulate ? kAddF32 : (y_dtype == kF32 ? kStoreF32 : kStoreBF16);
-    p.partials = nullptr;
-    p.tile_counters = nullptr;
     p.rows_a = pl.swapped ? N : M;
     p.rows_b = pl.swapped ? M : N;
-    if (pl.splits > 1) {
-        const size_t need = partial_bytes(pl, M, N);
-        const int tiles = ((p.rows_a + kBM - 1) / kBM) * ((p.rows_b + pl.bn - 1) / pl.bn);
-        if (workspace == nullptr || workspace_bytes < need || tile_counters == nullptr || counters_len < tiles) {
-            set_last_error("gemm_tc: a [%d, %d, %d] product splits K %d ways and needs %zu bytes of scratch and %d tile "
-                           "counters; %zu bytes and %d counters were given", M, N, K, pl.splits, need, tiles,
-                           workspace_bytes, counters_len);
-            return kTooLarge;
-        }
-        p.partials = (float*)workspace;
-        p.tile_counters = tile_counters;
-    }
     CUtensorMap ma, mb;
     int rc;
     if (pl.swapped) {

@@ -255,18 +255,16 @@ def sm_count(device) -> int:
 
 
 def gemm_tc_plan(M: int, N: int, K: int, device, force_splits: int = 0) -> dict:
-    """How the tensor-core product of this shape runs, and the scratch it needs when it splits K."""
-    swapped, bn, splits, counters = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-    need = ctypes.c_size_t()
-    lib().citlali_gemm_tc_plan(_i(M), _i(N), _i(K), _i(sm_count(device)), _i(force_splits), ctypes.byref(swapped), ctypes.byref(bn),
-                               ctypes.byref(splits), ctypes.byref(need), ctypes.byref(counters))
-    return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value, "workspace_bytes": need.value,
-            "tile_counters": counters.value}
+    """How the tensor-core product of this shape runs."""
+    swapped, bn, splits = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    lib().citlali_gemm_tc_plan(_i(M), _i(N), _i(K), _i(sm_count(device)), _i(force_splits), ctypes.byref(swapped),
+                               ctypes.byref(bn), ctypes.byref(splits))
+    return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value}
 
 
 def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
-    """One scratch buffer per device and purpose (split-K partials, split-context attention
-    partials); it only grows.  Kernels on one stream use it one after another."""
+    """One scratch buffer per device and purpose (split-context attention partials, argmax segments);
+    it only grows.  Kernels on one stream use it one after another."""
     key = (torch.device(device).index or 0, purpose)
     ws = _workspace.get(key)
     if ws is None or ws.numel() < nbytes:
@@ -275,26 +273,6 @@ def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
     return ws
-
-
-def _gemm_workspace(device, nbytes: int) -> torch.Tensor:
-    return _scratch(device, "gemm split-K", nbytes)
-
-
-_counters = {}
-
-
-def _gemm_counters(device, count: int) -> torch.Tensor:
-    """Arrival counters of the split-K product's output tiles: zero between launches (the kernel
-    leaves them so)."""
-    key = torch.device(device).index or 0
-    c = _counters.get(key)
-    if c is None or c.numel() < count:
-        require(not torch.cuda.is_current_stream_capturing(),
-                "the tile counters would have to grow during graph capture; run the step once before capturing")
-        c = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
-        _counters[key] = c
-    return c
 
 
 def gemm_tc_accepts(x, w, y) -> bool:
@@ -315,13 +293,6 @@ def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_spli
             and x.is_contiguous() and w.is_contiguous(),
             "gemm_tc: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
     require(y.shape == (M, N // 2 if swiglu else N), "gemm_tc: the output's shape does not fit")
-    plan = gemm_tc_plan(M, N, K, x.device, force_splits)
-    ws = counters = None
-    if plan["splits"] > 1:
-        ws = _gemm_workspace(x.device, plan["workspace_bytes"])
-        counters = _gemm_counters(x.device, plan["tile_counters"])
     mode = (1 if accumulate else 0) | (2 if swiglu else 0)
-    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode), _i(force_splits), _ptr(ws),
-                                 ctypes.c_size_t(ws.numel() if ws is not None else 0), _ptr(counters),
-                                 _i(counters.numel() if counters is not None else 0), _ptr(error_flag),
-                                 _i(sm_count(x.device)), _stream()), "gemm_tc")
+    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode),
+                                 _i(force_splits), _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")
