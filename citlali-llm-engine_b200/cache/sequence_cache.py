@@ -110,6 +110,7 @@ class SequenceCache:
             else:
                 raise CitlaliError(f"schedule step {step} asks for a cache of unknown kind {type(req).__name__}")
         pin = self.device.type == "cuda"
+        self._has_window = any(req.window is not None for req in by_kv)
         for req, steps in by_kv.items():
             shape = (len(steps), self.num_pages, req.num_kv_heads, page_size, req.head_dim)
             table_host = torch.zeros((num_slots, self.max_pages_per_slot), dtype=torch.int32, pin_memory=pin)
@@ -153,6 +154,9 @@ class SequenceCache:
         require(self.slots.is_held(slot), f"slot {slot} is not held")
         require(new_length <= self.max_sequence_tokens,
                 f"a sequence of {new_length} tokens exceeds the cache's limit of {self.max_sequence_tokens} per sequence")
+        have = self.lengths[slot]
+        if have > 0 and (new_length - 1) // self.page_size == (have - 1) // self.page_size:
+            return          # the page that holds the last token also holds the new ones
         need_index = (new_length + self.page_size - 1) // self.page_size
         plans = []
         for g in self.kv_groups:
@@ -180,6 +184,8 @@ class SequenceCache:
         """The step that wrote positions below ``new_length`` has been issued."""
         require(self.slots.is_held(slot), f"slot {slot} is not held")
         self.lengths[slot] = new_length
+        if not self._has_window:
+            return
         for g in self.kv_groups:
             w = g.requirement.window
             if w is None:

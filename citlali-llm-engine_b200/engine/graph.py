@@ -44,6 +44,7 @@ class DecodeGraphRunner:
         for s in self._sizes:
             self._offsets.append(self._offsets[-1] + (s + 3) // 4 * 4)
         self.ints_host = torch.zeros(self._offsets[-1], dtype=torch.int32, pin_memory=True)
+        self._ints_np = self.ints_host.numpy()           # the same pinned memory, written without tensor ops
         self.ints = torch.zeros(self._offsets[-1], dtype=torch.int32, device=dev)
         self.floats_host = torch.zeros((2, B), dtype=torch.float32, pin_memory=True)   # temperature, uniform
         self.floats = torch.zeros((2, B), dtype=torch.float32, device=dev)
@@ -103,18 +104,16 @@ class DecodeGraphRunner:
         """Write the step's inputs into the pinned mirror and issue the copies.  ``tokens`` None:
         keep the device's token buffer (fed from the last step's output on the device)."""
         n = len(slots)
-        h = self.ints_host
+        h, o = self._ints_np, self._offsets
         if tokens is not None:
-            self._piece(h, 0, n).copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
-        slot_t = torch.as_tensor(list(slots), dtype=torch.int32)
-        pos_t = torch.as_tensor(list(positions), dtype=torch.int32)
-        self._piece(h, 1, n).copy_(slot_t)
-        self._piece(h, 2, n).copy_(pos_t)
-        self._piece(h, 4, n).copy_(slot_t)
-        self._piece(h, 5, n).copy_(pos_t)
-        lo = 0 if tokens is not None else self._offsets[1]
-        hi = self._offsets[6]
-        self.ints[lo:hi].copy_(h[lo:hi], non_blocking=True)
+            h[o[0]:o[0] + n] = tokens
+        h[o[1]:o[1] + n] = slots
+        h[o[2]:o[2] + n] = positions
+        h[o[4]:o[4] + n] = slots
+        h[o[5]:o[5] + n] = positions
+        lo = 0 if tokens is not None else o[1]
+        hi = o[6]
+        self.ints[lo:hi].copy_(self.ints_host[lo:hi], non_blocking=True)
         if temperature > 0.0:
             self.floats_host[0, :n] = float(temperature)
             self.floats_host[1, :n] = torch.as_tensor(list(uniforms), dtype=torch.float32)
