@@ -202,19 +202,32 @@ attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunk
     }
 }
 
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One float at shared-memory address `addr` of the block with rank `rank` in this cluster.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // The same work on the tensor cores, for pages of 64 keys.  The rows of the MMA are the query
 // heads that share the key/value head (padded to 16), so a key or value read from the cache
 // serves all of them.  The block walks its chunk one page at a time (cp.async, double-buffered);
 // each warp takes 16 keys of the page: S = Q K^T (mma.sync m16n8k16), online softmax in float,
 // O += P V.  At the end the four warps' (m, l, O) are merged through shared memory and written
 // as the chunk's partial, maxima in log2 units.
-template <int D>
+template <int D, int kStagesKV>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                            const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                            const int32_t* __restrict__ page_table, int page_table_stride,
                            const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
-                           float* __restrict__ partial, int max_chunks, int chunk_pages, int nq, int nkv, int window,
+                           __nv_bfloat16* __restrict__ out, int out_stride, int nq, int nkv, int window,
                            float scale_log2) {
     using namespace fa;
     constexpr int kPage = 64;
@@ -223,11 +236,11 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     constexpr int kChunksPerRow = D / 8;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);          // 16 rows
-    const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + kKvStages * kTileBytes;
+    const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + kStagesKV * kTileBytes;
 
     dependents_may_launch();
     wait_for_predecessor();
-    const int chunk = blockIdx.x;
+    const int split = gridDim.x, rank = blockIdx.x;      // the blocks of a (sequence, head group) are one cluster
     const int group = nq / nkv;
     const int row_tiles = (group + 15) / 16;
     const int g = blockIdx.y / row_tiles;
@@ -236,9 +249,10 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int row = blockIdx.z;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int chunk_keys = chunk_pages * kPage;
-    if (chunk * chunk_keys > pos || chunk * chunk_keys + chunk_keys <= lo) return;
-    const int tile_lo = max(chunk * chunk_pages, lo / kPage), tile_hi = min(chunk * chunk_pages + chunk_pages - 1, pos / kPage);
+    // the visible pages are cut into `split` runs of equal length; this block takes run `rank` (it may be empty)
+    const int first_page = lo / kPage, last_page = pos / kPage;
+    const int per_block = (last_page - first_page + split) / split;
+    const int tile_lo = first_page + rank * per_block, tile_hi = min(tile_lo + per_block - 1, last_page);
     const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -257,13 +271,14 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             cp_async16(s_v + buf * kTileBytes + r * kRowBytes + ch * 16, v_pool + src);
         }
     };
-    load_tile(tile_lo, 0);
-    cp_async_commit();
-    if (tile_lo + 1 <= tile_hi) load_tile(tile_lo + 1, 1);
-    cp_async_commit();
+#pragma unroll
+    for (int ahead = 0; ahead < kStagesKV - 1; ++ahead) {
+        if (tile_lo + ahead <= tile_hi) load_tile(tile_lo + ahead, ahead);
+        cp_async_commit();
+    }
 
     uint32_t qf[D / 16][4];
-    cp_async_wait<2>();
+    cp_async_wait<kStagesKV - 1>();
     __syncthreads();
     {
         const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -278,10 +293,10 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
     for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-        const int buf = (tile - tile_lo) % kKvStages;
-        if (tile + 2 <= tile_hi) load_tile(tile + 2, (tile + 2 - tile_lo) % kKvStages);
+        const int buf = (tile - tile_lo) % kStagesKV;
+        if (tile + kStagesKV - 1 <= tile_hi) load_tile(tile + kStagesKV - 1, (tile + kStagesKV - 1 - tile_lo) % kStagesKV);
         cp_async_commit();
-        cp_async_wait<2>();
+        cp_async_wait<kStagesKV - 1>();
         __syncthreads();
         const uint32_t kb = s_k + buf * kTileBytes + warp * 16 * kRowBytes, vb = s_v + buf * kTileBytes + warp * 16 * kRowBytes;
         float s[2][4];
@@ -353,35 +368,75 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
     __syncthreads();
-    for (int e = tid; e < heads_here * (D + 2); e += 128) {
-        const int h = e / (D + 2), i = e % (D + 2);
-        float M = -INFINITY;
+    // the four warps' results folded into one (m, l, O) per head: first into registers, then over `park`
+    constexpr int kPerThread = (16 * (D + 2) + 127) / 128;
+    float folded[kPerThread];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, park[((size_t)w * 16 + h) * (D + 2)]);
-        float v;
-        if (i == 0) {
-            v = M;
-        } else {
-            v = 0.0f;
+    for (int k = 0; k < kPerThread; ++k) {
+        const int e = tid + 128 * k;
+        float v = 0.0f;
+        if (e < heads_here * (D + 2)) {
+            const int h = e / (D + 2), i = e % (D + 2);
+            float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float mw = park[((size_t)w * 16 + h) * (D + 2)];
-                const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
-                v = fmaf(park[((size_t)w * 16 + h) * (D + 2) + i], f, v);
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, park[((size_t)w * 16 + h) * (D + 2)]);
+            if (i == 0) {
+                v = M;
+            } else {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float mw = park[((size_t)w * 16 + h) * (D + 2)];
+                    const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
+                    v = fmaf(park[((size_t)w * 16 + h) * (D + 2) + i], f, v);
+                }
             }
         }
-        partial[(((size_t)row * nq + head0 + h) * max_chunks + chunk) * (D + 2) + i] = v;
+        folded[k] = v;
     }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+        const int e = tid + 128 * k;
+        if (e < heads_here * (D + 2)) park[e] = folded[k];          // [head][D + 2]
+    }
+    // Every block of the cluster now holds its run's (m, l, O) for each head.  After a cluster barrier
+    // block `rank` merges heads rank, rank + split, ... over all blocks, in rank order, reading the
+    // others' shared memory, and writes the output; a second barrier keeps that memory alive meanwhile.
+    __syncthreads();
+    if (split > 1) cluster_barrier();
+    const uint32_t part_addr = s_q + 16 * kRowBytes;
+    for (int h = rank; h < heads_here; h += split) {
+        const uint32_t head_addr = part_addr + (uint32_t)(h * (D + 2)) * 4u;
+        float M = -INFINITY;
+        for (int z = 0; z < split; ++z) M = fmaxf(M, ld_cluster_f32(head_addr, z));
+        float L = 0.0f;
+        for (int z = 0; z < split; ++z) {
+            const float mz = ld_cluster_f32(head_addr, z);
+            if (mz != -INFINITY) L = fmaf(ld_cluster_f32(head_addr + 4u, z), exp2f(mz - M), L);
+        }
+        const float inv = 1.0f / L;
+        for (int i = tid; i < D; i += 128) {
+            float a = 0.0f;
+            for (int z = 0; z < split; ++z) {
+                const float mz = ld_cluster_f32(head_addr, z);
+                if (mz != -INFINITY) a = fmaf(ld_cluster_f32(head_addr + (uint32_t)(2 + i) * 4u, z), exp2f(mz - M), a);
+            }
+            out[(size_t)row * out_stride + (size_t)(head0 + h) * D + i] = __float2bfloat16_rn(a * inv);
+        }
+    }
+    if (split > 1) cluster_barrier();
 }
 
-template <int D>
-static int launch_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
-                     int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, float* partial,
-                     int max_chunks, int chunk_pages, int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
-    constexpr int tiles = (16 + 2 * kKvStages * 64) * (D * 2 + 16);
+static int g_forced_split = 0;     // > 0: blocks per (sequence, head group), for tuning
+
+template <int D, int kStagesKV>
+static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                     int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
+                     int rows, int nq, int nkv, int window, float scale, int split, cudaStream_t stream) {
+    constexpr int tiles = (16 + 2 * kStagesKV * 64) * (D * 2 + 16);
     constexpr int park = 16 * (D * 2 + 16) + 4 * 16 * (D + 2) * 4;
     constexpr int smem = tiles > park ? tiles : park;
-    auto kernel = attention_decode_tc_kernel<D>;
+    auto kernel = attention_decode_tc_kernel<D, kStagesKV>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -389,11 +444,40 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
         configured = true;
     }
     const int group = nq / nkv;
-    dim3 grid(max_chunks, nkv * ((group + 15) / 16), rows);
-    launch_kernel(kernel, grid, 128, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
-                                        (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
-                                        partial, max_chunks, chunk_pages, nq, nkv, window, scale * 1.4426950408889634f);
+    const int kv_tiles = nkv * ((group + 15) / 16);
+    if (split > 8) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(split, kv_tiles, rows);
+    launch_kernel_clustered(kernel, grid, 128, smem, split, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
+                            (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
+                            (__nv_bfloat16*)out, out_stride, nq, nkv, window, scale * 1.4426950408889634f);
     return CITLALI_LAUNCH_CHECK();
+}
+
+// Blocks per (sequence, head group) = cluster size, and key/value tiles in flight per block.  Measured at
+// head size 128, 8 key/value heads, 4,096 cached tokens: one sequence 8 blocks, eight sequences 4, sixty-four
+// sequences 1 (no merging at all once the grid fills the GPU twice over).  The choice depends on the batch
+// alone, never on the sequences' lengths, so a captured launch stays valid.
+template <int D>
+static int launch_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
+                     int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
+                     int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
+    const int group = nq / nkv;
+    const long pairs = (long)rows * nkv * ((group + 15) / 16);
+    int split = 1;
+    for (int s = 8; s >= 2; s /= 2)
+        if (pairs * s <= 300) { split = s; break; }
+    if (g_forced_split > 0) split = g_forced_split;
+    // with at most one block per SM there is shared memory for six tiles in flight (head sizes up to 128)
+    if constexpr (D <= 128) {
+        if (pairs * split <= 80)          // more blocks than that, each filling an SM, no longer fit cluster by cluster
+            return launch_tc_stages<D, 6>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, out,
+                                          out_stride, rows, nq, nkv, window, scale, split, stream);
+    }
+    return launch_tc_stages<D, kKvStages>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, out,
+                                          out_stride, rows, nq, nkv, window, scale, split, stream);
 }
 
 template <int EPL, int GT>
@@ -431,6 +515,9 @@ static int pick_gt(int gt, const void* q, int q_stride, const void* k_pool, cons
 
 using namespace citlali;
 
+// > 0: the tensor-core kernel uses this many blocks per (sequence, head group) (1, 2, 4, 8 or 16); 0: its own choice.
+extern "C" void citlali_attention_decode_set_split(int split) { g_forced_split = split; }
+
 // Scratch for the partials of `rows` single-token rows whose positions stay below
 // `max_positions`: floats.
 extern "C" size_t citlali_attention_decode_scratch_floats(int rows, int nq, int head_dim, int page_size, int max_positions) {
@@ -467,29 +554,11 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         case 16: case 32: case 48: case 64: case 80: case 96: case 112: case 128: case 256: break;
         default: tensor_cores = false;
     }
-    // Pages per block.  The tensor-core kernel takes the smallest of 2, 4, 8, 16 that keeps the grid
-    // near two waves: few sequences get short chunks (enough blocks to fill the GPU), many sequences
-    // long ones (less merging).  The choice depends on the batch and the longest possible context
-    // only, not on the sequences' lengths, so a captured launch stays valid.
-    int chunk_pages = kChunkPages;
     if (tensor_cores) {
-        const int kv_tiles = nkv * ((group + 15) / 16);
-        const int max_pages = (max_positions + page_size - 1) / page_size;
-        chunk_pages = 16;
-        for (int c = 2; c <= 16; c *= 2)
-            if ((long long)rows * kv_tiles * ((max_pages + c - 1) / c) <= 300) { chunk_pages = c; break; }
-    }
-    const int chunk_keys = chunk_pages * page_size;
-    const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;
-    const size_t need = (size_t)rows * nq * max_chunks * (head_dim + 2);
-    if (partial == nullptr || partial_floats < need) {
-        set_last_error("attention_decode: %zu floats of scratch are needed, %zu were given", need, partial_floats);
-        return kTooLarge;
-    }
-    int rc = -1000;
-    if (tensor_cores) {
-#define CITLALI_TC(DD) case DD: rc = launch_tc<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, \
-                                                    partial, max_chunks, chunk_pages, rows, nq, nkv, window, scale, stream); break
+        // pages of 64 and a head size the tensor-core kernel has: its blocks merge their partial results
+        // through distributed shared memory, the scratch is not used
+#define CITLALI_TC(DD) case DD: return launch_tc<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, \
+                                                      out, out_stride, rows, nq, nkv, window, scale, stream)
         switch (head_dim) {
             CITLALI_TC(16); CITLALI_TC(32); CITLALI_TC(48); CITLALI_TC(64); CITLALI_TC(80); CITLALI_TC(96); CITLALI_TC(112);
             CITLALI_TC(128); CITLALI_TC(256);
@@ -497,8 +566,17 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         }
 #undef CITLALI_TC
     }
-    if (rc == -1000) {
-        // other head sizes and page sizes: the CUDA-core kernel
+    // other head sizes and page sizes: the CUDA-core kernel writes one partial per chunk of four pages to
+    // the scratch, and a second kernel merges them
+    const int chunk_keys = kChunkPages * page_size;
+    const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;
+    const size_t need = (size_t)rows * nq * max_chunks * (head_dim + 2);
+    if (partial == nullptr || partial_floats < need) {
+        set_last_error("attention_decode: %zu floats of scratch are needed, %zu were given", need, partial_floats);
+        return kTooLarge;
+    }
+    int rc = -1000;
+    {
         const int gt = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
         // elements per lane: the smallest of 1, 2, 4, 8 that covers the head with 32 lanes and divides it
         int epl = head_dim <= 32 ? 1 : head_dim <= 64 ? 2 : head_dim <= 128 ? 4 : 8;

@@ -47,7 +47,7 @@ def _stream():
 
 
 _launches = 0
-_KERNELS_PER_CALL = {"attention_decode": 2, "argmax_rows_wide": 2}
+_KERNELS_PER_CALL = {"attention_decode_merged": 2, "argmax_rows_wide": 2}
 
 
 def launch_count() -> int:
@@ -240,7 +240,10 @@ def attention_decode(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos,
         _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(row_slot), _ptr(row_pos), _ptr(out), _i(out.shape[1]), _ptr(ws), ctypes.c_size_t(ws.numel() // 4),
         _i(rows), _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(max_positions), _f(scale),
-        _stream()), "attention_decode")
+        _stream()),
+        # one kernel whose blocks merge through distributed shared memory, or a partial and a merge kernel
+        "attention_decode" if (page_size == 64 and q_stride % 8 == 0 and q.data_ptr() % 16 == 0
+                               and head_dim in (16, 32, 48, 64, 80, 96, 112, 128, 256)) else "attention_decode_merged")
 
 
 _sm_count = {}
