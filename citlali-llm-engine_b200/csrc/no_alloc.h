@@ -11,7 +11,9 @@
 //
 // It computes exactly what citlali_attention_decode computes, with the same kernels, but the
 // float scratch that holds the per-chunk partial results lives in a fixed array inside the
-// library instead of being passed in.
+// library instead of being passed in.  (For pages of 64 keys and the head sizes of the
+// tensor-core kernel the blocks exchange their partial results through shared memory and the
+// array is not touched; the limit below is checked all the same.)
 //
 //   Limit.  The array holds CITLALI_NO_ALLOC_SCRATCH_FLOATS floats (4 MiB).  A call needs
 //   rows * nq * ceil(max_positions / (2 * page_size)) * (head_dim + 2) floats; a call that

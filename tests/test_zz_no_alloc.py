@@ -53,8 +53,11 @@ def _no_alloc(lib, q, kp, vp, table, slots, pos, out, nq, nkv, d, page, max_posi
 def test_no_alloc_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
     lib = ops.lib()
     assert hasattr(lib, "citlali_attention_decode_no_alloc")
-    nq, nkv, d, page = 8, 2, 64, 64
-    for seed, lengths in ((1, [700, 3, 257, 64]), (2, [5, 130, 1, 300])):      # the second call sees stale scratch
+    nq, nkv, d = 8, 2, 64
+    # pages of 16 keys take the kernel pair that keeps per-chunk partials in the scratch array; pages of 64 take the
+    # cluster kernel, which leaves the array alone.  Within each pair the second call sees what the first one left.
+    for seed, lengths, page in ((1, [700, 3, 257, 64], 16), (2, [5, 130, 1, 300], 16),
+                                (3, [700, 3, 257, 64], 64), (4, [5, 130, 1, 300], 64)):
         q, kp, vp, table, slots, pos = _case(seed, lengths, nq, nkv, d, page)
         max_positions = table.shape[1] * page
         want = torch.empty(len(lengths), nq * d, dtype=torch.bfloat16, device=DEV)
