@@ -75,14 +75,18 @@ class InferenceSession:
         return self._finish(config, model, max_context, max_batch, max_tokens)
 
     def load_random(self, config, seed: int, max_context: int = 2048, dtype="bfloat16", device="cuda:0",
-                    max_batch: int = 8, max_tokens: Optional[int] = None, gain_spread: float = 0.0) -> "InferenceSession":
-        """Random weights made on the device, layer by layer, for measurements: nothing is
-        written and nothing can be compared with another reader of a folder."""
+                    max_batch: int = 8, max_tokens: Optional[int] = None, gain_spread: float = 0.0,
+                    stored_dtype=None) -> "InferenceSession":
+        """Random weights made on the device, tensor by tensor, for measurements and for tests at
+        sizes a folder would be too large for: nothing is written.  ``stored_dtype`` (default:
+        ``dtype``) is the precision the values are rounded to before the model takes them, as if
+        they had been stored so: two sessions with the same seed and ``stored_dtype`` hold the same
+        values whatever they compute in."""
         dev = _cuda_device(device)
         spec = config.to_model_spec()
         ctx = self._context(dev, dtype)
         model = DecoderModel(spec, ctx)
-        stored = parse_dtype(dtype)
+        stored = parse_dtype(stored_dtype if stored_dtype is not None else dtype)
         handles: Dict[str, WeightHandle] = {}
         for s in model.tensor_specs():
             if s.optional and spec.tie_head_to_embedding is not False:
