@@ -109,6 +109,149 @@ def plain_toy(w, tokens):
     return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["head.weight"])
 
 
+class Top1RoutedFeedForward:
+    """A feed-forward with routing: a router picks one of `experts` gated feed-forwards per token; the winner's
+    output is scaled by its softmax probability.  Router logits, softmax and the choice are float32."""
+
+    def __init__(self, params, prefix):
+        self.hidden, self.inter, self.experts = params["hidden_size"], params["intermediate_size"], params["experts"]
+        self.router = DenseLinear([f"{prefix}.router.weight"], [self.experts], self.hidden)
+        self.gate_up = [DenseLinear([f"{prefix}.experts.{e}.gate.weight", f"{prefix}.experts.{e}.up.weight"],
+                                    [self.inter, self.inter], self.hidden) for e in range(self.experts)]
+        self.down = [DenseLinear([f"{prefix}.experts.{e}.down.weight"], [self.hidden], self.inter) for e in range(self.experts)]
+
+    def tensor_specs(self):
+        return self.router.tensor_specs() + [t for l in self.gate_up + self.down for t in l.tensor_specs()]
+
+    def bind(self, weights, ctx):
+        for l in [self.router] + self.gate_up + self.down:
+            l.bind(weights, ctx)
+        self.dtype = ctx.dtype
+
+    def forward(self, h, batch, residual):
+        logits = self.router.forward(h, out_dtype=torch.float32)
+        prob = torch.softmax(logits, dim=-1)
+        choice = torch.argmax(logits, dim=-1)
+        for e in range(self.experts):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel() == 0:
+                continue
+            x = h[rows].contiguous()
+            gu = self.gate_up[e].forward(x, out_dtype=torch.float32)
+            act = (torch.nn.functional.silu(gu[:, :self.inter]) * gu[:, self.inter:]).to(self.dtype)
+            y = self.down[e].forward(act, out_dtype=torch.float32)
+            residual[rows] += y * prob[rows, e][:, None]
+        return residual
+
+
+class SlowedRotary:
+    """Another position encoding: the half-split rotation with every frequency divided by `factor`."""
+
+    def __init__(self, params, head_dim):
+        self.rotary_dim = head_dim
+        i = torch.arange(head_dim // 2, dtype=torch.float64)
+        self.inv_freq = (torch.pow(torch.tensor(float(params["theta"]), dtype=torch.float64), -2.0 * i / head_dim)
+                         / float(params["factor"])).to(torch.float32)
+
+
+@dataclasses.dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int
+    hidden_size: int
+    max_position_embeddings: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["vocab_size"], d["hidden_size"], d["max_position_embeddings"])
+
+    def to_dict(self):
+        return {"architectures": ["ToyRoutedForCausalLM"], **dataclasses.asdict(self)}
+
+    def to_model_spec(self):
+        H = self.hidden_size
+        norm = lambda p: cb.PartSpec("rms_norm", {"size": H, "eps": 1e-5}, p)
+        attn = {"hidden_size": H, "num_heads": 4, "num_kv_heads": 4, "head_dim": 16, "qk_norm_eps": None,
+                "position": {"kind": "slowed_rotary", "theta": 1e4, "factor": 4.0}, "window": 40}
+        routed = cb.PartSpec("top1_routed", {"hidden_size": H, "intermediate_size": 48, "experts": 3}, "l0.moe")
+        dense = cb.PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 96}, "l1.mlp")
+        layers = (
+            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", attn, "l0.attn"), routed, norm("l0.n1"), norm("l0.n2")),
+            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", dict(attn, window=None), "l1.attn"), dense,
+                         norm("l1.n1"), norm("l1.n2")),
+        )
+        return cb.ModelSpec("ToyRoutedForCausalLM", self.vocab_size, H, self.max_position_embeddings, "emb.weight",
+                            layers, (cb.ScheduleStep(0), cb.ScheduleStep(1)), norm("final"), "head.weight", None)
+
+
+def plain_routed(w, tokens):
+    T = len(tokens)
+    pos = list(range(T))
+    x = plain.embedding(w["emb.weight"], tokens)
+
+    def rotate(t):
+        d = t.shape[-1]
+        i = torch.arange(d // 2, dtype=torch.float64)
+        inv = (torch.pow(torch.tensor(1e4, dtype=torch.float64), -2.0 * i / d) / 4.0).to(torch.float32)
+        ang = (torch.tensor(pos, dtype=torch.float32)[:, None] * inv[None, :]).double()
+        c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = t[..., :d // 2], t[..., d // 2:]
+        return torch.cat([a * c - b * s_, a * s_ + b * c], dim=-1)
+
+    def attention(x, pre, window):
+        h = plain.rms_norm(x, w[f"{pre}.n1.weight"], 1e-5)
+        q = rotate(plain.linear(h, w[f"{pre}.attn.q_proj.weight"]).view(T, 4, 16))
+        k = rotate(plain.linear(h, w[f"{pre}.attn.k_proj.weight"]).view(T, 4, 16))
+        v = plain.linear(h, w[f"{pre}.attn.v_proj.weight"]).view(T, 4, 16)
+        return x + plain.linear(plain.causal_attention(q, k, v, 4, 4, window=window).reshape(T, 64), w[f"{pre}.attn.o_proj.weight"])
+
+    x = attention(x, "l0", 40)
+    h = plain.rms_norm(x, w["l0.n2.weight"], 1e-5)
+    logits = plain.linear(h, w["l0.moe.router.weight"])
+    prob = torch.softmax(logits, -1)
+    choice = torch.argmax(logits, -1)
+    margin = torch.topk(logits, 2, dim=-1).values
+    y = torch.zeros_like(x)
+    for t in range(T):
+        e = int(choice[t])
+        g = plain.linear(h[t:t + 1], w[f"l0.moe.experts.{e}.gate.weight"]); u = plain.linear(h[t:t + 1], w[f"l0.moe.experts.{e}.up.weight"])
+        y[t] = plain.linear(plain.swiglu(g, u), w[f"l0.moe.experts.{e}.down.weight"])[0] * prob[t, e]
+    x = x + y
+    x = attention(x, "l1", None)
+    x = x + plain.feed_forward(plain.rms_norm(x, w["l1.n2.weight"], 1e-5), w, "l1.mlp")
+    return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["emb.weight"]), (margin[:, 0] - margin[:, 1])
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward with routing, a position encoding of its own, a windowed and a full attention layer (two cache
+    groups), a head that is tied because the folder holds none: registered from here, replayed in 32-bit against the oracle."""
+    cb.register_part("feed_forward", "top1_routed", Top1RoutedFeedForward)
+    cb.register_part("position", "slowed_rotary", SlowedRotary)
+    cb.register_architecture("ToyRoutedForCausalLM", RoutedConfig)
+    try:
+        cfg = RoutedConfig(vocab_size=200, hidden_size=64, max_position_embeddings=256)
+        folder = cb.write_random_model(str(tmp_path / "routed"), cfg, seed=8, dtype="float32")
+        _, w = plain.load_folder(folder)
+        session = cb.InferenceSession().load_model(folder, max_context=256, dtype="float32", max_batch=2)
+        assert [g.requirement.window for g in session.cache.kv_groups] == [40, None] and session.runner is None
+        assert session.model.tied
+        import random
+        rng = random.Random(5)
+        reqs = [(f"m{i}", [rng.randrange(200) for _ in range(n)]) for i, n in enumerate([90, 12, 150])]
+        want = {rid: plain_routed(w, toks) for rid, toks in reqs}
+        for steps in (replay.whole(reqs), replay.tail(reqs), replay.batched(reqs, [60, 12, 1], 2)):
+            got = replay.run_in_process(session, steps)
+            for (rid, pos), row in got.items():
+                ref, margins = want[rid]
+                if float(margins[:pos + 1].min()) < 1e-4:
+                    continue                   # a routing near-tie upstream: either expert is a right answer
+                assert (row.double() - ref[pos]).abs().max() <= 2e-5 * ref[pos].abs().max() + 1e-6
+        assert session.cache.pages_held() == 0
+    finally:
+        cb.unregister_part("feed_forward", "top1_routed")
+        cb.unregister_part("position", "slowed_rotary")
+        cb.unregister_architecture("ToyRoutedForCausalLM")
+
+
 @pytest.fixture
 def toy_registered():
     cb.register_part("mixer", "running_mean", RunningMeanMixer)
