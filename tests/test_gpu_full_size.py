@@ -96,3 +96,13 @@ def test_replayed_decode_steps_equal_plain_steps_at_production_shapes(sessions):
     for s in slots:
         s16.release(s)
     assert [r.tokens for r in res] == outs
+
+
+def test_generation_at_production_shapes_repeats_bit_for_bit(sessions):
+    _, s16 = sessions
+    vocab = SHAPE["vocab_size"]
+    prompts = [random_tokens(vocab, n, 30 + n) for n in (200, 64, 1, 333)]
+    opts = cb.GenerationOptions(max_new_tokens=96, max_context=1024, stop_ids=[], temperature=0.7, seed=3)
+    a = [r.tokens for r in s16.generate(prompts, opts)]
+    b = [r.tokens for r in s16.generate(prompts, opts)]
+    assert a == b and all(len(t) == 96 for t in a)

@@ -114,3 +114,21 @@ def test_command_line(model_dirs, tmp_path):
     assert info.returncode == 0 and "hidden_size: 64" in info.stdout and "vocab_size: 512" in info.stdout
     bad = subprocess.run([sys.executable, cli, "--model", model, "--frobnicate"], capture_output=True, text=True, timeout=120)
     assert bad.returncode == 1 and "unknown argument: --frobnicate" in bad.stderr
+
+
+def test_long_generation_repeats_bit_for_bit_with_and_without_graphs(model_dirs):
+    """300 decode steps at batch 4, twice through the replayed graph and once with plain launches: every kernel
+    waits for its predecessor before touching shared buffers, so nothing may differ."""
+    cfg = TINY["D"]
+    prompts = [random_tokens(cfg["vocab_size"], n, 60 + n) for n in (5, 90, 31, 200)]
+    opts = cb.GenerationOptions(max_new_tokens=300, max_context=1024, stop_ids=[])
+    session = cb.InferenceSession().load_model(model_dirs[("D", "bfloat16")], max_context=1024, dtype="bfloat16", max_batch=4)
+    assert session.runner is not None
+    first = [r.tokens for r in session.generate(prompts, opts)]
+    second = [r.tokens for r in session.generate(prompts, opts)]
+    assert first == second and all(len(t) == 300 for t in first)
+    plain_launches = cb.InferenceSession()
+    plain_launches.use_graphs = False
+    plain_launches.load_model(model_dirs[("D", "bfloat16")], max_context=1024, dtype="bfloat16", max_batch=4)
+    assert plain_launches.runner is None
+    assert [r.tokens for r in plain_launches.generate(prompts, opts)] == first
