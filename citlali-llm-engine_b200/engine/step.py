@@ -35,8 +35,6 @@ def pack_step(entries: List[StepEntry], past: List[int], vocab_size: int, device
         for w in e.want:
             require(0 <= w < len(e.tokens),
                     f"slot {e.slot}: logits asked at place {w} of {len(e.tokens)} tokens")
-        for t in e.tokens:
-            require(0 <= int(t) < vocab_size, f"token id {t} out of vocab range [0, {vocab_size})")
         rows += len(e.tokens)
     B = len(entries)
     wanted = sum(len(e.want) for e in entries)
@@ -53,7 +51,11 @@ def pack_step(entries: List[StepEntry], past: List[int], vocab_size: int, device
     w = 0
     for b, e in enumerate(entries):
         n = len(e.tokens)
-        tokens[r:r + n] = torch.as_tensor(list(e.tokens), dtype=torch.int32)
+        ids = torch.as_tensor(list(e.tokens), dtype=torch.int64)
+        if int(ids.min()) < 0 or int(ids.max()) >= vocab_size:        # as the reference checks (qwen_model.cpp:240-241)
+            bad = int(ids[(ids < 0) | (ids >= vocab_size)][0])
+            require(False, f"token id {bad} out of vocab range [0, {vocab_size})")
+        tokens[r:r + n] = ids.to(torch.int32)
         row_slot[r:r + n] = e.slot
         row_pos[r:r + n] = torch.arange(past[b], past[b] + n, dtype=torch.int32)
         seq_start[b] = r
