@@ -1,23 +1,28 @@
 // Causal attention of runs of new tokens over the paged cache on the fifth-generation tensor
 // cores, for head size 128 and pages of 64 keys.
 //
-// A block takes 128 consecutive new tokens of one sequence and one query head and walks the
-// visible keys 128 at a time (two cache pages).  Three roles run concurrently:
-//   warp 4, one lane: TMA producer.  The query tile once, then a key tile and a value tile at a
-//                     time (128-byte swizzle; a tile is two 64-wide halves of the head); the next
-//                     key tile is fetched as soon as the scores of the current one are computed.
-//   warp 5, one lane: MMA issuer.  S = Q K^T (tcgen05.mma, both operands K-major in shared
-//                     memory) into tensor memory; O += P V with P read from tensor memory (it
-//                     overwrites the first half of S) and V, as stored (head dimension
-//                     contiguous), as an MN-major shared-memory operand.
-// A block needs 97 KB of shared memory and 256 columns of tensor memory, so two blocks share an SM:
-// while one block's softmax warps work, the other block's MMAs run.
-//   warps 0-3:        softmax.  Each thread owns one query row: it reads its 128 scores from
-//                     tensor memory, keeps the running reference maximum and sum in float
-//                     (no shuffles), writes P as bfloat16 back to tensor memory, and rescales
-//                     its row of O only when the maximum has grown by more than 2^8 (the sum
-//                     uses the same reference, so the result is exact).  At the end it divides
-//                     its row of O by the sum and stores it.
+// A block owns an SM and works on TWO query tiles of 128 rows that read the same keys and values:
+// two query heads of one key/value group over the same 128 new tokens (when the group has an even
+// number of heads), else two consecutive row tiles of one head.  It walks the visible keys 128 at
+// a time (two cache pages); each key and value tile is fetched once for both query tiles, which
+// halves the traffic from L2, the resource this kernel is otherwise bound by.  Roles:
+//   warps 8, 9, one lane each: TMA producers of the key and of the value tiles (128-byte swizzle; a
+//                     tile is two 64-wide halves of the head), two tiles deep.
+//   warp 10, one lane: MMA issuer for both query tiles.  S = Q K^T (tcgen05.mma, both operands
+//                     K-major in shared memory) into tensor memory; O += P V with P read from tensor
+//                     memory (it overwrites the first half of S) and V, as stored (head dimension
+//                     contiguous), as an MN-major shared-memory operand.  The scores of a query
+//                     tile's next key tile are issued right after its P V, so one query tile's
+//                     softmax runs while the other's MMAs do.
+//   warps 0-3, 4-7:   softmax of query tile 0 and 1.  Each thread owns one query row.  Exponentials
+//                     are taken against the reference the row already has, without a maximum: the
+//                     reference only has to keep P and the sums in range, and the tile's sum tells
+//                     whether it did.  If it did not (or the row has no reference yet: the first
+//                     tile), the warp takes a second pass with the true maximum and rescales its
+//                     rows of O.  The sum uses the same reference, so the result is exact.  At the
+//                     end the thread divides its row of O by the sum and stores it.
+// Tensor memory: 512 columns, per query tile 128 of scores / P and 128 of output.  Shared memory:
+// two query tiles, two key tiles, two value tiles of 32 KB.
 //
 // Formulas: the reference's (attention_scores_kernel / attention_values_kernel,
 // src/compute/cuda/kernels.cu:545-649): s = q.k / sqrt(d), keys lo..p for the token at position
@@ -33,11 +38,12 @@ namespace fatc {
 using namespace tc;
 
 constexpr int kD = 128, kTileQ = 128, kTileK = 128, kPage = 64;
-constexpr int kThreads = 192;
+constexpr int kWarpLoadK = 8, kWarpLoadV = 9, kWarpMma = 10;
+constexpr int kThreads = 352;
 constexpr uint32_t kHalfTile = 128 * 128;              // bytes of [128 rows x 64 bfloat16]
 constexpr uint32_t kTileBytes = 2 * kHalfTile;         // [128 x 128] bfloat16
-// tensor memory columns
-constexpr uint32_t kColS = 0, kColP = 0, kColO = 128, kTmemCols = 256;     // P overwrites the scores it came from
+// tensor memory columns of query tile b: kSubCols * b + ...; P overwrites the scores it came from
+constexpr uint32_t kSubCols = 256, kColS = 0, kColP = 0, kColO = 128, kTmemCols = 512;
 
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
@@ -67,6 +73,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+// Waits for this thread's tensor-memory loads; the 32 registers go through the statement so that
+// nothing that uses them is scheduled before it.
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -103,36 +119,45 @@ struct Params {
     const int32_t* seq_start; const int32_t* seq_slot; const int32_t* seq_past;
     __nv_bfloat16* out; int out_stride;
     int nq, nkv, window;
+    int pair_heads;                      // 1: the two query tiles are heads 2x, 2x+1; 0: row tiles 2y, 2y+1 of head x
     float scale_log2;
     int32_t* error_flag;
 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+// One of the block's two query tiles: its head, its first row within the sequence's new tokens, and the
+// key tiles it reads (none when it has no rows).
+struct QueryTile {
+    int head, q0, tile_lo, tile_hi;
+    __device__ bool reads(int t) const { return t >= tile_lo && t <= tile_hi; }
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Params p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t q_bar, k_full, v_full, k_empty, v_empty, s_full, p_full, o_done;
+    __shared__ __align__(8) uint64_t q_bar, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
     volatile int* abort_flag = &abort_word;
 
-    dependents_may_launch();
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t s_q = base, s_k = base + kTileBytes, s_v = s_k + kTileBytes;
+    const uint32_t s_q = base, s_k = base + 2 * kTileBytes, s_v = base + 4 * kTileBytes;      // two tiles each
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         abort_word = 0;
         mbar_init(smem_u32(&q_bar), 1);
-        mbar_init(smem_u32(&k_full), 1); mbar_init(smem_u32(&v_full), 1);
-        mbar_init(smem_u32(&k_empty), 1); mbar_init(smem_u32(&v_empty), 1);
-        mbar_init(smem_u32(&s_full), 1);
-        mbar_init(smem_u32(&p_full), 4);
-        mbar_init(smem_u32(&o_done), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&k_full[i]), 1); mbar_init(smem_u32(&v_full[i]), 1);
+            mbar_init(smem_u32(&k_empty[i]), 1); mbar_init(smem_u32(&v_empty[i]), 1);
+            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&p_full[i]), 4);
+            mbar_init(smem_u32(&o_done[i]), 1);
+        }
         fence_barrier_init();
         fence_async_proxy();
     }
-    if (warp == 5) {
+    if (warp == kWarpMma) {
         tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
         tmem_relinquish();
     }
@@ -140,181 +165,275 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    dependents_may_launch();                                 // only now: this block holds its tensor memory
 
     wait_for_predecessor();                                  // everything below reads what earlier kernels wrote
-    // blocks are handed out x fastest: all heads of the last query tile (the one that sees the most
-    // keys) first, then all heads of the tile before it, and so on
-    const int seq = blockIdx.z, head = blockIdx.x;
+    // blocks are handed out x fastest: all heads of the last rows (the ones that see the most keys)
+    // first, then all heads of the rows before them, and so on
+    const int seq = blockIdx.z;
     const int row0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - row0;
-    const int q0 = (gridDim.y - 1 - blockIdx.y) * kTileQ;
-    const bool active = q0 < n_new;
     const int past = p.seq_past[seq];
-    const int g = head / (p.nq / p.nkv);
+    const int y = gridDim.y - 1 - blockIdx.y;
+    QueryTile qt[2];
+    int t_lo = INT_MAX, t_hi = -1, last_key = -1;            // the block's key tiles and its last visible key
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        qt[b].head = p.pair_heads ? 2 * blockIdx.x + b : blockIdx.x;
+        qt[b].q0 = (p.pair_heads ? y : 2 * y + b) * kTileQ;
+        if (qt[b].q0 < n_new) {
+            const int first_pos = past + qt[b].q0, last_pos = past + min(qt[b].q0 + kTileQ, n_new) - 1;
+            const int lo_key = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+            qt[b].tile_lo = lo_key / kTileK; qt[b].tile_hi = last_pos / kTileK;
+            t_lo = min(t_lo, qt[b].tile_lo); t_hi = max(t_hi, qt[b].tile_hi); last_key = max(last_key, last_pos);
+        } else {
+            qt[b].tile_lo = 0; qt[b].tile_hi = -1;
+        }
+    }
+    const int g = qt[0].head / (p.nq / p.nkv);               // both query tiles read this key/value head
     const int32_t* pages = p.page_table + (size_t)p.seq_slot[seq] * p.page_table_stride;
-    const int first_pos = past + q0, last_pos = past + min(q0 + kTileQ, n_new) - 1;
-    const int lo_key = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-    const int tile_lo = lo_key / kTileK, tile_hi = last_pos / kTileK;
-    const int tiles = active ? tile_hi - tile_lo + 1 : 0;
 
-    if (warp == 4) {
-        if (lane == 0 && active) {
-            mbar_arrive_expect_tx(smem_u32(&q_bar), kTileBytes);
-            tma_load_2d(s_q, &map_q, head * kD, row0 + q0, smem_u32(&q_bar));
-            tma_load_2d(s_q + kHalfTile, &map_q, head * kD + 64, row0 + q0, smem_u32(&q_bar));
-            for (int t = 0; t < tiles; ++t) {
-                const int key0 = (tile_lo + t) * kTileK;
+    if (warp == kWarpLoadK || warp == kWarpLoadV) {
+        if (lane == 0 && t_hi >= t_lo) {
+            const bool is_k = warp == kWarpLoadK;
+            if (is_k) {
+                // rows past the end of q read as zeros; a query tile without rows is loaded and never used
+                mbar_arrive_expect_tx(smem_u32(&q_bar), 2 * kTileBytes);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    tma_load_2d(s_q + b * kTileBytes, &map_q, qt[b].head * kD, row0 + qt[b].q0, smem_u32(&q_bar));
+                    tma_load_2d(s_q + b * kTileBytes + kHalfTile, &map_q, qt[b].head * kD + 64, row0 + qt[b].q0, smem_u32(&q_bar));
+                }
+            }
+            const CUtensorMap* map = is_k ? &map_k : &map_v;
+            for (int t = t_lo; t <= t_hi; ++t) {
+                const int i = t - t_lo, st = i & 1;
+                const int key0 = t * kTileK;
                 // two pages per tile; a page that lies wholly past the last visible key is not fetched (the
                 // first page stands in): its scores are masked and its values are multiplied by zeros
                 const int page_a = pages[key0 / kPage];
-                const bool second = key0 + kPage <= last_pos;
+                const bool second = key0 + kPage <= last_key;
                 const int page_b = second ? pages[key0 / kPage + 1] : page_a;
                 const int ra = (page_a * p.nkv + g) * kPage, rb = (page_b * p.nkv + g) * kPage;
-                const uint32_t kb = smem_u32(&k_full), vb = smem_u32(&v_full);
-                if (!mbar_wait(smem_u32(&k_empty), (t & 1u) ^ 1u, abort_flag, p.error_flag, 201)) break;
-                mbar_arrive_expect_tx(kb, kTileBytes);
-                tma_load_2d(s_k, &map_k, 0, ra, kb);
-                tma_load_2d(s_k + 64 * 128, &map_k, 0, rb, kb);
-                tma_load_2d(s_k + kHalfTile, &map_k, 64, ra, kb);
-                tma_load_2d(s_k + kHalfTile + 64 * 128, &map_k, 64, rb, kb);
-                if (!mbar_wait(smem_u32(&v_empty), (t & 1u) ^ 1u, abort_flag, p.error_flag, 210)) break;
-                mbar_arrive_expect_tx(vb, kTileBytes);
-                tma_load_2d(s_v, &map_v, 0, ra, vb);
-                tma_load_2d(s_v + 64 * 128, &map_v, 0, rb, vb);
-                tma_load_2d(s_v + kHalfTile, &map_v, 64, ra, vb);
-                tma_load_2d(s_v + kHalfTile + 64 * 128, &map_v, 64, rb, vb);
+                const uint32_t full = smem_u32(is_k ? &k_full[st] : &v_full[st]);
+                const uint32_t empty = smem_u32(is_k ? &k_empty[st] : &v_empty[st]);
+                const uint32_t dst = (is_k ? s_k : s_v) + st * kTileBytes;
+                if (!mbar_wait(empty, ((i >> 1) & 1u) ^ 1u, abort_flag, p.error_flag, is_k ? 201 : 210)) break;
+                mbar_arrive_expect_tx(full, kTileBytes);
+                tma_load_2d(dst, map, 0, ra, full);
+                tma_load_2d(dst + 64 * 128, map, 0, rb, full);
+                tma_load_2d(dst + kHalfTile, map, 64, ra, full);
+                tma_load_2d(dst + kHalfTile + 64 * 128, map, 64, rb, full);
             }
         }
         __syncwarp();
-    } else if (warp == 5) {
-        if (lane == 0 && active) {
+    } else if (warp == kWarpMma) {
+        if (lane == 0 && t_hi >= t_lo) {
             constexpr uint32_t idesc_qk = instr_desc_bf16(kTileQ, kTileK);
             constexpr uint32_t idesc_pv = instr_desc_bf16(kTileQ, kD) | (1u << 16);        // B is MN-major
+            bool ok = true;
+            int k_ready = t_lo - 1, v_ready = t_lo - 1;       // key / value tiles whose arrival this thread has seen
             // MMAs of one thread run in the order they are issued, so the scores of tile t+1, issued after
-            // P V of tile t, overwrite P only when that product has read it
-            auto issue_qk = [&]() {
+            // P V of tile t, overwrite P only when that product has read it.
+            auto issue_qk = [&](int b, int t) {
+                const int st = (t - t_lo) & 1;
+                if (k_ready < t) {
+                    if (!mbar_wait(smem_u32(&k_full[st]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 203)) { ok = false; return; }
+                    tc_fence_after();
+                    k_ready = t;
+                }
+                const uint32_t q_tile = s_q + b * kTileBytes, k_tile = s_k + st * kTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t half = (ks >> 2) * kHalfTile, off = (ks & 3) * 32;
-                    mma_bf16(tmem + kColS, smem_desc_sw128(s_q + half, off), smem_desc_sw128(s_k + half, off),
+                    mma_bf16(tmem + b * kSubCols + kColS, smem_desc_sw128(q_tile + half, off), smem_desc_sw128(k_tile + half, off),
                              idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                mma_commit(smem_u32(&k_empty));
-                mma_commit(smem_u32(&s_full));
+                mma_commit(smem_u32(&s_full[b]));
             };
-            bool ok = mbar_wait(smem_u32(&q_bar), 0, abort_flag, p.error_flag, 202);
-            if (ok) ok = mbar_wait(smem_u32(&k_full), 0, abort_flag, p.error_flag, 203);
-            if (ok) { tc_fence_after(); issue_qk(); }
-            for (int t = 0; t < tiles && ok; ++t) {
-                if (!mbar_wait(smem_u32(&p_full), t & 1u, abort_flag, p.error_flag, 205)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&v_full), t & 1u, abort_flag, p.error_flag, 206)) { ok = false; break; }
-                tc_fence_after();
+            ok = mbar_wait(smem_u32(&q_bar), 0, abort_flag, p.error_flag, 202);
 #pragma unroll
-                for (int j = 0; j < kTileK / 16; ++j)
-                    mma_bf16_ts(tmem + kColO, tmem + kColP + j * 8, smem_desc_mn_sw128(s_v + j * 16 * 128, kHalfTile), idesc_pv,
-                                (t > 0 || j > 0) ? 1u : 0u);
-                mma_commit(smem_u32(&v_empty));
-                mma_commit(smem_u32(&o_done));
-                if (t + 1 < tiles) {
-                    if (!mbar_wait(smem_u32(&k_full), (t + 1) & 1u, abort_flag, p.error_flag, 204)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_qk();
+            for (int b = 0; b < 2; ++b)
+                if (ok && qt[b].reads(t_lo)) issue_qk(b, t_lo);
+            if (ok) mma_commit(smem_u32(&k_empty[0]));
+            for (int t = t_lo; t <= t_hi && ok; ++t) {
+                const int st = (t - t_lo) & 1;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    if (!ok) break;
+                    if (qt[b].reads(t)) {
+                        const int j = t - qt[b].tile_lo;      // this query tile's own count of key tiles
+                        if (!mbar_wait(smem_u32(&p_full[b]), j & 1u, abort_flag, p.error_flag, 205)) { ok = false; break; }
+                        if (v_ready < t) {
+                            if (!mbar_wait(smem_u32(&v_full[st]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 206)) { ok = false; break; }
+                            v_ready = t;
+                        }
+                        tc_fence_after();
+                        const uint32_t v_tile = s_v + st * kTileBytes;
+#pragma unroll
+                        for (int jj = 0; jj < kTileK / 16; ++jj)
+                            mma_bf16_ts(tmem + b * kSubCols + kColO, tmem + b * kSubCols + kColP + jj * 8,
+                                        smem_desc_mn_sw128(v_tile + jj * 16 * 128, kHalfTile), idesc_pv, (j > 0 || jj > 0) ? 1u : 0u);
+                        mma_commit(smem_u32(&o_done[b]));
+                    }
+                    if (b == 1) mma_commit(smem_u32(&v_empty[st]));
+                    if (t + 1 <= t_hi && qt[b].reads(t + 1)) issue_qk(b, t + 1);
+                    if (b == 1 && t + 1 <= t_hi && ok) mma_commit(smem_u32(&k_empty[st ^ 1]));
                 }
             }
         }
         __syncwarp();
-    } else if (active) {
-        // softmax: this thread owns query row `r`
-        const int r = warp * 32 + lane;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        const int pos = past + q0 + r;
+    } else {
+        // softmax of query tile b: this thread owns its row `r`
+        const int b = warp >> 2, quarter = warp & 3;
+        const QueryTile me = b ? qt[1] : qt[0];
+        const int tiles = me.tile_hi - me.tile_lo + 1;        // 0 for a query tile without rows
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t sub = tmem + b * kSubCols + lane_addr;
+        const int pos = past + me.q0 + r;
         const int lo = p.window > 0 ? pos - p.window + 1 : 0;
+        const int warp_pos = past + me.q0 + quarter * 32;
         float m_ref = -INFINITY, l = 0.0f;                    // reference maximum (raw score units) and sum
         bool ok = true;
         for (int t = 0; t < tiles && ok; ++t) {
-            const int key0 = (tile_lo + t) * kTileK;
-            const uint32_t s_addr = tmem + lane_addr + kColS;
-            if (!mbar_wait(smem_u32(&s_full), t & 1u, abort_flag, p.error_flag, 207)) { ok = false; break; }
+            const int key0 = (me.tile_lo + t) * kTileK;
+            const uint32_t s_addr = sub + kColS;
+            if (!mbar_wait(smem_u32(&s_full[b]), t & 1u, abort_flag, p.error_flag, 207)) { ok = false; break; }
             tc_fence_after();
-            const bool masked = key0 + kTileK - 1 > past + q0 + warp * 32 || (p.window > 0 && key0 < past + q0 + warp * 32 + 31 - p.window + 1);
-            // The row's 128 scores, 64 at a time to keep registers for two blocks per SM: maximum of the
-            // first half (dropped), then the second half (kept), then the first half again.
-            uint32_t lo_half[64], hi_half[64];
-            auto load_half = [&](uint32_t* dst, int c_base) {
-                tmem_ld32(s_addr + c_base, dst);
-                tmem_ld32(s_addr + c_base + 32, dst + 32);
-                tmem_ld_wait();
-                if (masked) {
+            const bool masked = key0 + kTileK - 1 > warp_pos || (p.window > 0 && key0 < warp_pos + 31 - p.window + 1);
+            uint32_t pk[64];                                  // P of this row, two bfloat16 a register
+            bool two_pass = t == 0;
+            if (!two_pass) {
+                // One pass, 32 scores at a time while the next 32 are on their way from tensor memory.  A P above
+                // 2^15 makes the sum exceed 2^15, and a sum above 2^15 needs a P above 2^8: past that the
+                // reference is renewed.  The scores stay in tensor memory until P is stored over them.
+                const float ref = m_ref == -INFINITY ? 0.0f : m_ref * p.scale_log2;
+                float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+                uint32_t a[32], bb[32];
+                auto chunk = [&](uint32_t* h, int c_base, uint32_t* dst) {
+                    if (masked) {
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) {
-                        const int key = key0 + c_base + c;
-                        if (key > pos || key < lo) dst[c] = 0xff800000u;          // -inf
+                        for (int c = 0; c < 32; ++c) {
+                            const int key = key0 + c_base + c;
+                            if (key > pos || key < lo) h[c] = 0xff800000u;            // -inf
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        float e[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(__uint_as_float(h[c + i]), p.scale_log2, -ref));
+                        s0 += e[0] + e[1]; s1 += e[2] + e[3]; s2 += e[4] + e[5]; s3 += e[6] + e[7];
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(e[i], e[i + 1]);
+                            dst[(c + i) >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                    }
+                };
+                tmem_ld32(s_addr, a);
+                tmem_ld_wait32(a);
+                tmem_ld32(s_addr + 32, bb);
+                chunk(a, 0, pk);
+                tmem_ld_wait32(bb);
+                tmem_ld32(s_addr + 64, a);
+                chunk(bb, 32, pk + 16);
+                tmem_ld_wait32(a);
+                tmem_ld32(s_addr + 96, bb);
+                chunk(a, 64, pk + 32);
+                tmem_ld_wait32(bb);
+                chunk(bb, 96, pk + 48);
+                const float tile_sum = (s0 + s1) + (s2 + s3);
+                const bool in_range = tile_sum <= 32768.0f && m_ref != -INFINITY;      // false for inf and NaN too
+                two_pass = __any_sync(0xffffffffu, !in_range);
+                if (!two_pass) l += tile_sum;
+            }
+            if (two_pass) {
+                // The row's maximum first, 64 scores at a time (the first half is dropped and read again),
+                // then the exponentials against a reference that grows only when the maximum has run away
+                // from it by more than 2^8.
+                uint32_t h[64];
+                auto load_half = [&](int c_base) {
+                    tmem_ld32(s_addr + c_base, h);
+                    tmem_ld32(s_addr + c_base + 32, h + 32);
+                    tmem_ld_wait32(h);
+                    tmem_ld_wait32(h + 32);
+                    if (masked) {
+#pragma unroll
+                        for (int c = 0; c < 64; ++c) {
+                            const int key = key0 + c_base + c;
+                            if (key > pos || key < lo) h[c] = 0xff800000u;            // -inf
+                        }
+                    }
+                };
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+                load_half(0);
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) { mx0 = fmaxf(mx0, __uint_as_float(h[c])); mx1 = fmaxf(mx1, __uint_as_float(h[c + 1])); }
+                load_half(64);
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) { mx0 = fmaxf(mx0, __uint_as_float(h[c])); mx1 = fmaxf(mx1, __uint_as_float(h[c + 1])); }
+                const float mx = fmaxf(mx0, mx1);
+                float alpha = 1.0f;
+                const bool grow = (mx - m_ref) * p.scale_log2 > 8.0f || m_ref == -INFINITY;
+                if (grow && mx > -INFINITY) {
+                    alpha = m_ref == -INFINITY ? 0.0f : ex2((m_ref - mx) * p.scale_log2);
+                    m_ref = mx;
+                    l *= alpha;
+                }
+                const bool rescale = t > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
+                const float ref = m_ref == -INFINITY ? 0.0f : m_ref * p.scale_log2;
+                float sum0 = 0.0f, sum1 = 0.0f;
+                auto exp_pack = [&](uint32_t* dst) {              // 64 scores -> 32 registers of two bfloat16
+#pragma unroll
+                    for (int c = 0; c < 64; c += 4) {
+                        const float e0 = ex2(fmaf(__uint_as_float(h[c]), p.scale_log2, -ref));
+                        const float e1 = ex2(fmaf(__uint_as_float(h[c + 1]), p.scale_log2, -ref));
+                        const float e2 = ex2(fmaf(__uint_as_float(h[c + 2]), p.scale_log2, -ref));
+                        const float e3 = ex2(fmaf(__uint_as_float(h[c + 3]), p.scale_log2, -ref));
+                        sum0 += e0 + e1; sum1 += e2 + e3;
+                        __nv_bfloat162 h01 = __floats2bfloat162_rn(e0, e1), h23 = __floats2bfloat162_rn(e2, e3);
+                        dst[c >> 1] = *reinterpret_cast<uint32_t*>(&h01);
+                        dst[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h23);
+                    }
+                };
+                exp_pack(pk + 32);
+                load_half(0);
+                exp_pack(pk);
+                l += sum0 + sum1;
+                // O must be quiet before it is rescaled (P V of the tile before has ended by then anyway: the
+                // scores of this tile were issued after it)
+                if (rescale) {
+                    if (!mbar_wait(smem_u32(&o_done[b]), (t - 1) & 1u, abort_flag, p.error_flag, 208)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kD; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(sub + kColO + c0, v);
+                        tmem_ld_wait32(v);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                        tmem_st32(sub + kColO + c0, v);
                     }
                 }
-            };
-            float mx = -INFINITY;
-            load_half(lo_half, 0);
-#pragma unroll
-            for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(lo_half[c]));
-            load_half(hi_half, 64);
-#pragma unroll
-            for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(hi_half[c]));
-            // grow the reference only when the maximum has run away by more than 2^8
-            float alpha = 1.0f;
-            const bool grow = (mx - m_ref) * p.scale_log2 > 8.0f || m_ref == -INFINITY;
-            if (grow && mx > -INFINITY) {
-                alpha = m_ref == -INFINITY ? 0.0f : ex2((m_ref - mx) * p.scale_log2);
-                m_ref = mx;
-                l *= alpha;
             }
-            const bool rescale = t > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
-            const float ref = m_ref == -INFINITY ? 0.0f : m_ref * p.scale_log2;
-            float sum = 0.0f;
-            auto exp_pack = [&](uint32_t* h) {                // 64 scores -> 32 registers of two bfloat16
-#pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    const float a = ex2(fmaf(__uint_as_float(h[c]), p.scale_log2, -ref));
-                    const float b = ex2(fmaf(__uint_as_float(h[c + 1]), p.scale_log2, -ref));
-                    sum += a + b;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
-                    h[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-            };
-            exp_pack(hi_half);
-            load_half(lo_half, 0);
-            exp_pack(lo_half);
-            l += sum;
-            // O must be quiet before it is rescaled (P V of the tile before has ended by then anyway: the
-            // scores of this tile were issued after it)
-            if (rescale) {
-                if (!mbar_wait(smem_u32(&o_done), (t - 1) & 1u, abort_flag, p.error_flag, 208)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll 1
-                for (int c0 = 0; c0 < kD; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem + lane_addr + kColO + c0, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-                    tmem_st32(tmem + lane_addr + kColO + c0, v);
-                }
-            }
-            tmem_st32(tmem + lane_addr + kColP, lo_half);
-            tmem_st32(tmem + lane_addr + kColP + 32, hi_half);
+            tmem_st32(sub + kColP, pk);
+            tmem_st32(sub + kColP + 32, pk + 32);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[b]));
         }
-        if (ok && tiles > 0 && mbar_wait(smem_u32(&o_done), (tiles - 1) & 1u, abort_flag, p.error_flag, 209)) {
+        if (ok && tiles > 0 && mbar_wait(smem_u32(&o_done[b]), (tiles - 1) & 1u, abort_flag, p.error_flag, 209)) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const bool store = q0 + r < n_new;
-            __nv_bfloat16* dst = p.out + (size_t)(row0 + q0 + r) * p.out_stride + (size_t)head * kD;
+            const bool store = me.q0 + r < n_new;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + me.q0 + r) * p.out_stride + (size_t)me.head * kD;
 #pragma unroll 1
             for (int c0 = 0; c0 < kD; c0 += 32) {
                 uint32_t ov[32];
-                tmem_ld32(tmem + lane_addr + kColO + c0, ov);
-                tmem_ld_wait();
+                tmem_ld32(sub + kColO + c0, ov);
+                tmem_ld_wait32(ov);
                 if (store) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
@@ -333,7 +452,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kWarpMma) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -420,16 +539,19 @@ extern "C" int citlali_attention_prefill_tc(const void* q, int q_stride, int tot
     p.seq_start = seq_start; p.seq_slot = seq_slot; p.seq_past = seq_past;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
     p.nq = nq; p.nkv = nkv; p.window = window;
+    // two heads of a key/value group share a block when groups have an even number of heads, else two row tiles
+    p.pair_heads = (nq / nkv) % 2 == 0 ? 1 : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_flag = error_flag;
-    const size_t smem = (size_t)3 * fatc::kTileBytes + 1024;
+    const size_t smem = (size_t)6 * fatc::kTileBytes + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fatc::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(nq, (max_new + fatc::kTileQ - 1) / fatc::kTileQ, sequences);
+    const int row_tiles = (max_new + fatc::kTileQ - 1) / fatc::kTileQ;
+    dim3 grid(p.pair_heads ? nq / 2 : nq, p.pair_heads ? row_tiles : (row_tiles + 1) / 2, sequences);
     launch_kernel(fatc::attention_prefill_tc_kernel, grid, fatc::kThreads, smem, stream, mq, mk, mv, p);
     return CITLALI_LAUNCH_CHECK();
 }
