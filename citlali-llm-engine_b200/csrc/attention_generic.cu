@@ -110,6 +110,103 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
     }
 }
 
+// The same for bfloat16 rows whose half head is a power-of-two number of 16-byte pieces (head sizes
+// 16, 32, 64, 128, 256): `lanes` = head_dim / 16 neighbouring lanes share a head, each with eight
+// elements of the first half and the eight they pair with in the second, moved as 16-byte words.
+constexpr int kRopeVecThreads = 128;
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 w;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return w;
+}
+
+template <typename TG>
+__global__ void __launch_bounds__(kRopeVecThreads)
+qk_norm_rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
+                              const float* __restrict__ inv_freq,
+                              const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                              const int32_t* __restrict__ page_table, int page_table_stride,
+                              __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int page_size,
+                              int nq, int nkv, int d, float eps, int write_cache, int heads_per_block, int lanes) {
+    extern __shared__ float2 cos_sin[];                 // [d / 2]: the row's rotation, shared by the block's heads
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x;
+    const int total = nq + 2 * nkv;
+    const int head_begin = blockIdx.y * heads_per_block;
+    const int head_end = min(total, head_begin + heads_per_block);
+    const int half = d >> 1;
+    const int pos = row_pos[row];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        cos_sin[i] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    size_t page_off = 0;
+    if (write_cache) {
+        const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
+        page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * d;       // + kv head * page_size * d
+    }
+    __nv_bfloat16* row_ptr = qkv + (size_t)row * total * d;
+    const int part = threadIdx.x % lanes, e0 = part * 8;      // this lane's elements e0..e0+7 of each half
+    const int heads_per_pass = kRopeVecThreads / lanes;
+    for (int h0 = head_begin; h0 < head_end; h0 += heads_per_pass) {      // the same trip count for every lane
+        const int head = h0 + threadIdx.x / lanes;
+        const bool on = head < head_end;
+        float x0[8], x1[8];
+        if (on) {
+            unpack8(*reinterpret_cast<const uint4*>(row_ptr + (size_t)head * d + e0), x0);
+            unpack8(*reinterpret_cast<const uint4*>(row_ptr + (size_t)head * d + half + e0), x1);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x0[i] = x1[i] = 0.0f;
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { ss = fmaf(x0[i], x0[i], ss); ss = fmaf(x1[i], x1[i], ss); }
+        for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!on) continue;
+        if (head >= nq + nkv) {                         // a value head goes to the cache as it is
+            if (write_cache) {
+                __nv_bfloat16* dst = v_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+                *reinterpret_cast<uint4*>(dst + e0) = pack8(x0);
+                *reinterpret_cast<uint4*>(dst + half + e0) = pack8(x1);
+            }
+            continue;
+        }
+        const bool is_q = head < nq;
+        if (!is_q && !write_cache) continue;
+        const TG* gain = is_q ? q_gain : k_gain;
+        if (gain) {
+            const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x0[i] = x0[i] * inv * ldf(gain, e0 + i);
+                x1[i] = x1[i] * inv * ldf(gain, half + e0 + i);
+            }
+        }
+        float y0[8], y1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 cs = cos_sin[e0 + i];
+            y0[i] = x0[i] * cs.x - x1[i] * cs.y;
+            y1[i] = x0[i] * cs.y + x1[i] * cs.x;
+        }
+        __nv_bfloat16* dst = is_q ? row_ptr + (size_t)head * d : k_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+        *reinterpret_cast<uint4*>(dst + e0) = pack8(y0);
+        *reinterpret_cast<uint4*>(dst + half + e0) = pack8(y1);
+    }
+}
+
 // One block per (row, query head).  Query head j reads KV head j / (nq / nkv)
 // (attention_scores_kernel, kernels.cu:564-565).  Keys lo..pos of the row's slot:
 //   s_t = (q . k_t) * scale;  m = max s_t;  e_t = exp(s_t - m);  Z = sum e_t;
@@ -212,6 +309,21 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
     if (grid.y > 65535) {
         set_last_error("qk_norm_rope_cache: too many heads (%d)", total);
         return kTooLarge;
+    }
+    // bfloat16 with a power-of-two number of 16-byte pieces in half a head: the kernel that moves 16-byte words
+    const int lanes = head_dim / 16;
+    if (dtype == kBF16 && head_dim % 16 == 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 &&
+        ((uintptr_t)qkv & 15u) == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0) {
+        const int per_pass = kRopeVecThreads / lanes;
+        const int vec_heads = rows >= 128 ? total : per_pass;
+        dim3 vec_grid(rows, (total + vec_heads - 1) / vec_heads);
+        return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
+            launch_kernel(qk_norm_rope_cache_vec_kernel<TG>, vec_grid, kRopeVecThreads, (size_t)(head_dim / 2) * sizeof(float2), stream,
+                (__nv_bfloat16*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, row_slot, row_pos, page_table,
+                page_table_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache,
+                vec_heads, lanes);
+            return CITLALI_LAUNCH_CHECK();
+        });
     }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
