@@ -108,6 +108,15 @@ int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, in
 // error_flag[1..2] receive the code and block of a wait that ran out.
 int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                     int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream);
+// The same product on pairs of SMs (tcgen05.mma with cta_group::2: a [256 x BN] tile per cluster of two
+// blocks, each fetching half of both operands).  Measured equal to the one-block kernel at 2,048 rows
+// (both run into the power limit), so it is off unless citlali_gemm_tc_set_pair_rows names a number of
+// rows of x from which citlali_gemm_tc uses it (0: never), on devices that run such clusters;
+// citlali_gemm_tc_pair_plan gives the tile width and the pairs that run at once.
+int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                         int mode, int32_t* error_flag, cudaStream_t stream);
+int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs);
+int citlali_gemm_tc_set_pair_rows(int rows);
 
 #ifdef __cplusplus
 }

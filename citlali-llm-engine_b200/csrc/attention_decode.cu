@@ -221,6 +221,47 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
 // each warp takes 16 keys of the page: S = Q K^T (mma.sync m16n8k16), online softmax in float,
 // O += P V.  At the end the four warps' (m, l, O) are merged through shared memory and written
 // as the chunk's partial, maxima in log2 units.
+constexpr int kMaxClusterBlocks = 16;     // blocks per (sequence, head group): a cluster, at most the non-portable size
+
+// Block `rank` of a cluster merges heads rank, rank + split, ... over the (m, l, O) that every block of
+// the cluster holds at `part_addr`, in rank order.  All blocks' (m, l) are read at once, then all their
+// values of an output element at once: the loads of a round are independent, so a round costs one trip
+// through the cluster, not one per block.
+template <int kBlocks, int D>
+__device__ __forceinline__ void merge_cluster_heads(uint32_t part_addr, __nv_bfloat16* out_row, int rank, int split, int heads_here, int tid) {
+    for (int h = rank; h < heads_here; h += split) {
+        const uint32_t head_addr = part_addr + (uint32_t)(h * (D + 2)) * 4u;
+        float mz[kBlocks], wz[kBlocks];
+#pragma unroll
+        for (int z = 0; z < kBlocks; ++z) {
+            mz[z] = z < split ? ld_cluster_f32(head_addr, z) : -INFINITY;
+            wz[z] = z < split ? ld_cluster_f32(head_addr + 4u, z) : 0.0f;           // l for now
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int z = 0; z < kBlocks; ++z) M = fmaxf(M, mz[z]);
+        float L = 0.0f;
+#pragma unroll
+        for (int z = 0; z < kBlocks; ++z) {
+            const float f = mz[z] == -INFINITY ? 0.0f : exp2f(mz[z] - M);
+            if (mz[z] != -INFINITY) L = fmaf(wz[z], f, L);
+            wz[z] = f;
+        }
+        const float inv = 1.0f / L;
+        for (int i = tid; i < D; i += 128) {
+            float v[kBlocks];
+#pragma unroll
+            for (int z = 0; z < kBlocks; ++z)
+                v[z] = (z < split && mz[z] != -INFINITY) ? ld_cluster_f32(head_addr + (uint32_t)(2 + i) * 4u, z) : 0.0f;
+            float a = 0.0f;
+#pragma unroll
+            for (int z = 0; z < kBlocks; ++z)
+                if (z < split && mz[z] != -INFINITY) a = fmaf(v[z], wz[z], a);
+            out_row[(size_t)h * D + i] = __float2bfloat16_rn(a * inv);
+        }
+    }
+}
+
 template <int D, int kStagesKV>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -239,7 +280,6 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + kStagesKV * kTileBytes;
 
     dependents_may_launch();
-    wait_for_predecessor();
     const int split = gridDim.x, rank = blockIdx.x;      // the blocks of a (sequence, head group) are one cluster
     const int group = nq / nkv;
     const int row_tiles = (group + 15) / 16;
@@ -256,12 +296,6 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
-    for (int c = tid; c < 16 * kChunksPerRow; c += 128) {
-        const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
-        if (r < heads_here) cp_async16(s_q + r * kRowBytes + ch * 16, q + (size_t)row * q_stride + (size_t)(head0 + r) * D + ch * 8);
-        else *reinterpret_cast<uint4*>(smem + r * kRowBytes + ch * 16) = make_uint4(0, 0, 0, 0);
-    }
-    cp_async_commit();
     auto load_tile = [&](int tile, int buf) {
         const size_t base = ((size_t)pages[tile] * nkv + g) * kPage * D;
         for (int c = tid; c < kPage * kChunksPerRow; c += 128) {
@@ -271,14 +305,29 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             cp_async16(s_v + buf * kTileBytes + r * kRowBytes + ch * 16, v_pool + src);
         }
     };
+    // Positions and page tables come from the host before the step, and every page but the row's last
+    // holds keys and values of earlier steps only.  Unless the row's last page is among this block's
+    // first tiles, they are fetched while the kernel ahead of this one (which writes the new token's
+    // key, value and query) is still running.
+    const bool early = tile_lo + kStagesKV - 2 < last_page;
+    auto first_tiles = [&]() {
 #pragma unroll
-    for (int ahead = 0; ahead < kStagesKV - 1; ++ahead) {
-        if (tile_lo + ahead <= tile_hi) load_tile(tile_lo + ahead, ahead);
-        cp_async_commit();
+        for (int ahead = 0; ahead < kStagesKV - 1; ++ahead) {
+            if (tile_lo + ahead <= tile_hi) load_tile(tile_lo + ahead, ahead);
+            cp_async_commit();
+        }
+    };
+    if (early) first_tiles();
+    wait_for_predecessor();
+    for (int c = tid; c < 16 * kChunksPerRow; c += 128) {
+        const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (r < heads_here) w = *reinterpret_cast<const uint4*>(q + (size_t)row * q_stride + (size_t)(head0 + r) * D + ch * 8);
+        *reinterpret_cast<uint4*>(smem + r * kRowBytes + ch * 16) = w;
     }
+    if (!early) first_tiles();
 
     uint32_t qf[D / 16][4];
-    cp_async_wait<kStagesKV - 1>();
     __syncthreads();
     {
         const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -405,25 +454,16 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __syncthreads();
     if (split > 1) cluster_barrier();
     const uint32_t part_addr = s_q + 16 * kRowBytes;
-    for (int h = rank; h < heads_here; h += split) {
-        const uint32_t head_addr = part_addr + (uint32_t)(h * (D + 2)) * 4u;
-        float M = -INFINITY;
-        for (int z = 0; z < split; ++z) M = fmaxf(M, ld_cluster_f32(head_addr, z));
-        float L = 0.0f;
-        for (int z = 0; z < split; ++z) {
-            const float mz = ld_cluster_f32(head_addr, z);
-            if (mz != -INFINITY) L = fmaf(ld_cluster_f32(head_addr + 4u, z), exp2f(mz - M), L);
+    __nv_bfloat16* out_row = out + (size_t)row * out_stride + (size_t)head0 * D;
+    if (split == 1) {
+        for (int e = tid; e < heads_here * D; e += 128) {
+            const int h = e / D, i = e % D;
+            out_row[(size_t)h * D + i] = __float2bfloat16_rn(park[h * (D + 2) + 2 + i] * (1.0f / park[h * (D + 2) + 1]));
         }
-        const float inv = 1.0f / L;
-        for (int i = tid; i < D; i += 128) {
-            float a = 0.0f;
-            for (int z = 0; z < split; ++z) {
-                const float mz = ld_cluster_f32(head_addr, z);
-                if (mz != -INFINITY) a = fmaf(ld_cluster_f32(head_addr + (uint32_t)(2 + i) * 4u, z), exp2f(mz - M), a);
-            }
-            out[(size_t)row * out_stride + (size_t)(head0 + h) * D + i] = __float2bfloat16_rn(a * inv);
-        }
-    }
+    } else if (split <= 2) merge_cluster_heads<2, D>(part_addr, out_row, rank, split, heads_here, tid);
+    else if (split <= 4) merge_cluster_heads<4, D>(part_addr, out_row, rank, split, heads_here, tid);
+    else if (split <= 8) merge_cluster_heads<8, D>(part_addr, out_row, rank, split, heads_here, tid);
+    else merge_cluster_heads<kMaxClusterBlocks, D>(part_addr, out_row, rank, split, heads_here, tid);
     if (split > 1) cluster_barrier();
 }
 
@@ -469,7 +509,7 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
     int split = 1;
     for (int s = 8; s >= 2; s /= 2)
         if (pairs * s <= 300) { split = s; break; }
-    if (g_forced_split > 0) split = g_forced_split;
+    if (g_forced_split > 0) split = g_forced_split > kMaxClusterBlocks ? kMaxClusterBlocks : g_forced_split;
     // with at most one block per SM there is shared memory for six tiles in flight (head sizes up to 128)
     if constexpr (D <= 128) {
         if (pairs * split <= 80)          // more blocks than that, each filling an SM, no longer fit cluster by cluster

@@ -15,9 +15,11 @@
 // rows of x ("normal": prompts) the MMA's 128-row operand is x and the BN-row operand is w.
 // With few rows ("swapped": decoding) the 128-row operand is w, so the weights stream through
 // the wide side at full rate and the few rows of x are the narrow side; K is then split over
-// several blocks so that every SM streams weights, each writing a float32 partial, and a second
-// kernel adds the partials in split order.  The split depends on the shape alone, never on the
-// batch, so a row's result does not depend on what else is in the step.
+// several blocks so that every SM streams weights.  The splits of a tile are one thread-block
+// cluster: each block sends its float32 partial sums through distributed shared memory to the
+// block that owns that part of the tile, which adds them in split order and writes the result.
+// The split depends on the shape alone, never on the batch, so a row's result does not depend
+// on what else is in the step.
 //
 // Every wait on an mbarrier gives up after a time limit, raises the error word and makes the
 // block leave through the normal exit (TMEM freed, copies in flight awaited).
@@ -52,104 +54,18 @@ struct GemmParams {
 
 template <int BN>
 constexpr int stages_for(bool swapped) {
-    // swapped (decoding): two blocks per SM, about 100 KB each; normal: one block of 192 KB
-    return swapped ? (BN <= 16 ? 6 : BN <= 32 ? 5 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
+    // swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
+    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of 192 KB
+    return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
 }
 
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
-// Four floats at shared-memory address `addr` of the block with rank `rank` in this cluster.
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
     float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
     return v;
-}
-
-// Split K: the blocks of a cluster hold one partial each of the same tile, [column][128 rows] floats at
-// shared-memory address `part_addr`.  Only the swapped form splits K: the tile's 128 rows are output
-// features n, its BN columns are rows m of x.  An item is four consecutive n of one m; the block with
-// rank r takes items r*128 .., (r + splits)*128 .., its 128 epilogue threads kItems of them at a time.
-// Every sum runs in rank (= split) order, whichever block computes it.
-template <int BN, int kItems, bool kGate>
-__device__ __forceinline__ void finish_cluster_tile(const GemmParams& p, uint32_t part_addr, int n_tile, int m_tile, int rank, int et) {
-    float* outf = (float*)p.out;
-    __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
-    const int half_n = p.N >> 1;
-#pragma unroll 1
-    for (int item0 = rank * 128 + et; item0 < BN * 32; item0 += 128 * p.splits * kItems) {
-        float4 a[kItems], u[kItems];
-        uint32_t src[kItems];
-        bool on[kItems];
-#pragma unroll
-        for (int k = 0; k < kItems; ++k) {
-            const int item = item0 + 128 * p.splits * k;
-            const int c = item >> 5, l4 = item & 31;
-            on[k] = item < BN * 32 && m_tile + c < p.M && n_tile + 4 * l4 < p.N && !(kGate && (l4 & 4));
-            src[k] = part_addr + (uint32_t)(c * kBM + 4 * l4) * 4u;
-            a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-            u[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll 1
-        for (int z0 = 0; z0 < p.splits; z0 += 4) {
-            float4 t[kItems][4], tu[kGate ? kItems : 1][4];
-#pragma unroll
-            for (int k = 0; k < kItems; ++k)
-#pragma unroll
-                for (int z = 0; z < 4; ++z) {
-                    const bool live = on[k] && z0 + z < p.splits;
-                    t[k][z] = live ? ld_cluster_f4(src[k], z0 + z) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (kGate) tu[k][z] = live ? ld_cluster_f4(src[k] + 64u, z0 + z) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-            for (int k = 0; k < kItems; ++k)
-#pragma unroll
-                for (int z = 0; z < 4; ++z) {
-                    a[k].x += t[k][z].x; a[k].y += t[k][z].y; a[k].z += t[k][z].z; a[k].w += t[k][z].w;
-                    if (kGate) { u[k].x += tu[k][z].x; u[k].y += tu[k][z].y; u[k].z += tu[k][z].z; u[k].w += tu[k][z].w; }
-                }
-        }
-#pragma unroll
-        for (int k = 0; k < kItems; ++k) {
-            if (!on[k]) continue;
-            const int item = item0 + 128 * p.splits * k;
-            const int m = m_tile + (item >> 5), n0 = n_tile + 4 * (item & 31);
-            const float v[4] = {a[k].x, a[k].y, a[k].z, a[k].w};
-            if (kGate) {
-                const float uu[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
-                const size_t o = (size_t)m * half_n + (n0 >> 5) * 16 + (n0 & 15);
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (n0 + e < p.N) outh[o + e] = __float2bfloat16_rn(silu_mul(v[e], uu[e]));
-                continue;
-            }
-            const size_t o = (size_t)m * p.N + n0;
-            if (n0 + 4 <= p.N && (p.N & 3) == 0) {
-                if (p.out_kind == kStoreBF16) {
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-                    *reinterpret_cast<uint2*>(outh + o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                } else {
-                    float4 w = a[k];
-                    if (p.out_kind == kAddF32) {
-                        const float4 old = *reinterpret_cast<const float4*>(outf + o);
-                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
-                    }
-                    *reinterpret_cast<float4*>(outf + o) = w;
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (n0 + e < p.N) {
-                        if (p.out_kind == kStoreBF16) outh[o + e] = __float2bfloat16_rn(v[e]);
-                        else if (p.out_kind == kAddF32) outf[o + e] += v[e];
-                        else outf[o + e] = v[e];
-                    }
-            }
-        }
-    }
 }
 
 template <int BN, bool kSwapped>
@@ -171,6 +87,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;            // tile storage starts on a 1024-byte boundary
     const uint32_t smem_a = tiles, smem_b = tiles + kStages * kBytesA;
+    // Split K: where the other blocks of the cluster put their partial sums of this block's share of the
+    // tile.  Behind the ring for narrow tiles; over the ring for wide ones, which then need a cluster
+    // barrier between the last MMA of every block and the first partial sent.
+    constexpr bool kRecvInRing = BN >= 64;
+    const uint32_t recv = kRecvInRing ? tiles : tiles + kStages * (kBytesA + kBytesB);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -391,12 +312,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             decode(u, ta, tb, sp);
             const int kb0 = sp * kb_per_split, kb1 = min(kblocks, kb0 + kb_per_split);
             const int as = acc_it % kAccStages;
-            if (!mbar_wait(smem_u32(&acc_full_bar[as]), (acc_it / kAccStages) & 1u, abort_flag, p.error_flag, 104)) break;
+            const bool acc_ready = mbar_wait(smem_u32(&acc_full_bar[as]), (acc_it / kAccStages) & 1u, abort_flag, p.error_flag, 104);
+            // (a split tile is its block's only unit: every thread of the cluster passes here exactly once)
+            if (kSwapped && kRecvInRing && p.splits > 1) cluster_sync_all();
+            if (!acc_ready) break;
             tc_fence_after();
             const int i = ta * kBM + quarter * 32 + lane;     // row of the 128-row operand
             const bool empty_range = kb1 <= kb0;              // a split that got no K blocks contributes zeros
-            // split K: this block's partial goes to its own shared memory, [column][128 rows], over the drained tile ring
-            float* part = reinterpret_cast<float*>(smem_raw + (tiles - raw));
+            // Split K (swapped form only; `sp` is this block's rank in the cluster of the tile's splits).  The
+            // tile is cut into units of four columns (rows m of x) and 32 rows (output features n: a warp's
+            // lanes); unit u belongs to the block with rank u % splits, and every block sends its partial
+            // of a unit to the owner's receive area, slot [sender][u / splits][lane][4 columns].
+            const int units_per_owner = (BN + p.splits - 1) / p.splits;
+            const bool pow2 = (p.splits & (p.splits - 1)) == 0;     // the plan's splits are; a forced split may not be
+            const int shift = 31 - __clz(p.splits);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
@@ -406,9 +335,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int c = 0; c < 16; ++c) v[c] = empty_range ? 0.0f : __uint_as_float(r[c]);
                 if (p.splits > 1) {
-                    float* dst = part + (size_t)c0 * kBM + quarter * 32 + lane;
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) dst[(size_t)c * kBM] = v[c];
+                    for (int c = 0; c < 16; c += 4) {
+                        const int unit = (c0 + c) + quarter;                 // = ((c0 + c) / 4) * 4 + quarter
+                        const int owner = pow2 ? (unit & (p.splits - 1)) : unit % p.splits;
+                        const int ul = pow2 ? (unit >> shift) : unit / p.splits;
+                        const uint32_t slot = recv + (uint32_t)(((sp * units_per_owner + ul) * 32 + lane) * 16);
+                        st_cluster_f4(cluster_addr(slot, (uint32_t)owner), v[c], v[c + 1], v[c + 2], v[c + 3]);
+                    }
                 } else {
                     finish(v, i, tb * BN + c0, c0);
                 }
@@ -420,21 +354,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
 
-    if (p.splits > 1) {
-        // The `splits` blocks of a tile form a cluster (rank = split).  Each has its partial in shared memory;
-        // after a cluster barrier every block adds up a share of the tile, reading all partials through
-        // distributed shared memory in rank order, and writes that share.  A second barrier keeps every
-        // block's shared memory alive until all have read it.
-        __syncthreads();
+    if (kSwapped && kRecvInRing && p.splits > 1 && warp < 2) cluster_sync_all();      // the barrier the epilogue warps pass after the last MMA
+    if (kSwapped && p.splits > 1) {
+        // The `splits` blocks of a tile form a cluster (rank = split).  Once every block has sent its partials
+        // (the cluster barrier makes them visible), each block adds up the units it owns, in rank order
+        // whatever the batch, and writes them.  Nothing reads another block's shared memory after the
+        // barrier, so the blocks leave without a second one.
         cluster_sync_all();
         if (warp >= 2) {
             int ta, tb, sp;
             decode(blockIdx.x, ta, tb, sp);
-            const uint32_t part_addr = tiles;
-            if (p.out_kind == kSwigluBF16) finish_cluster_tile<BN, 2, true>(p, part_addr, ta * kBM, tb * BN, sp, threadIdx.x - 64);
-            else finish_cluster_tile<BN, 2, false>(p, part_addr, ta * kBM, tb * BN, sp, threadIdx.x - 64);
+            const int units_per_owner = (BN + p.splits - 1) / p.splits;
+            float* outf = (float*)p.out;
+            __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
+#pragma unroll 1
+            for (int ul = warp - 2; ul < units_per_owner; ul += 4) {
+                const int unit = ul * p.splits + sp;
+                if (unit >= BN) break;
+                const int m0 = tb * BN + (unit >> 2) * 4, n = ta * kBM + (unit & 3) * 32 + lane;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int src = 0; src < p.splits; ++src) {
+                    const float4 t = ld_shared_f4(recv + (uint32_t)(((src * units_per_owner + ul) * 32 + lane) * 16));
+                    a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+                }
+                const float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int m = m0 + e;
+                    if (p.out_kind == kSwigluBF16) {
+                        // lanes 0-15 hold gate values, lanes 16-31 the up values of the same outputs
+                        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+                        if ((lane & 16) == 0 && n < p.N && m < p.M)
+                            outh[(size_t)m * (p.N >> 1) + (n >> 5) * 16 + (lane & 15)] = __float2bfloat16_rn(silu_mul(v[e], other));
+                    } else if (n < p.N && m < p.M) {
+                        const size_t o = (size_t)m * p.N + n;
+                        if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[e]);
+                        else if (p.out_kind == kAddF32) outf[o] += v[e];
+                        else outf[o] = v[e];
+                    }
+                }
+            }
         }
-        cluster_sync_all();
     }
 
     tc_fence_before();
@@ -534,7 +494,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
 template <int BN, bool kSwapped>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
     constexpr int stages = stages_for<BN>(kSwapped);
-    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + (kSwapped && BN < 64 ? BN * 512 + 4096 : 0) + 1024;      // ring, split-K receive area behind it, alignment
     auto kernel = gemm_tc_kernel<BN, kSwapped>;
     static bool configured = false;
     if (!configured) {
@@ -556,6 +516,13 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 
 using namespace citlali;
 using namespace citlali::tc;
+
+static int g_pair_rows = 0;      // > 0: from this many rows of x on, the product runs on pairs of SMs
+
+extern "C" int citlali_gemm_tc_set_pair_rows(int rows) {
+    g_pair_rows = rows;
+    return 0;
+}
 
 // How the product of this shape would run: *swapped, *bn and the K split (*splits).
 extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits) {
@@ -600,6 +567,11 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
     }
     if (sm_count <= 0) sm_count = 148;
     const Plan pl = make_plan(M, N, K, sm_count, force_splits);
+    if (!pl.swapped && g_pair_rows > 0 && M >= g_pair_rows) {
+        int bn = 0, pairs = 0;
+        citlali_gemm_tc_pair_plan(M, N, K, &bn, &pairs);
+        if (pairs > 0) return citlali_gemm_tc_pair(x, w, y, y_dtype, M, N, K, mode, error_flag, stream);
+    }
     GemmParams p;
     p.M = M; p.N = N; p.K = K;
     p.splits = pl.splits;

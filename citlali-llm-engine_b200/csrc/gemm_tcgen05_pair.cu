@@ -1,0 +1,376 @@
+// y[M, N] = x[M, K] . w[N, K]^T in bfloat16 for many rows of x (prompts), with two SMs on one tile.
+//
+// The blocks of a cluster of two share [256 x BN] output tiles: tcgen05.mma with cta_group::2, issued
+// by the block with cluster rank 0, multiplies 256 rows of x (128 from each block's shared memory)
+// by BN rows of w (BN / 2 from each block's shared memory) into the tensor memory of both blocks,
+// each holding its 128 rows of the accumulator.  Per K block a block therefore fetches 128 rows of x
+// and only half of the weight tile, which is what bounds the one-block kernel: its shared memory
+// takes the TMA writes and feeds the tensor core's reads of both whole operands.
+// Roles in each block (as in the one-block kernel):
+//   warp 0, one lane: TMA producer of this block's halves.  The bytes of both blocks are counted on
+//                     the full barrier of the block with rank 0; neither load is multicast.
+//   warp 1:           allocates tensor memory (both blocks, together); in the block with rank 0 one
+//                     lane issues the MMAs; tcgen05.commit arrives on the barriers of both blocks.
+//   warps 2-5:        epilogue of this block's 128 rows; the accumulator stage is handed back on a
+//                     barrier of the block with rank 0 on which the warps of both blocks arrive.
+// Every wait on an mbarrier gives up after a time limit, raises the error word and makes the block
+// leave through the normal exit (cluster barrier, tensor memory freed).
+#include "api.h"
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace citlali {
+namespace tc {
+namespace pair {
+
+constexpr int kBM = 128, kBK = 64, kAccStages = 2;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+struct Params {
+    void* out;
+    int out_kind;
+    int M, N, K;
+    int32_t* error_flag;
+};
+
+template <int BN>
+constexpr int stages_for() { return BN <= 192 ? 7 : 6; }      // 16 KB of x and BN * 64 bytes of w a stage
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Params p) {
+    constexpr int kStages = stages_for<BN>();
+    constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = (BN / 2) * kBK * 2;
+    constexpr uint32_t kIdesc = instr_desc_bf16(2 * kBM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full_bar[kAccStages], acc_empty_bar[kAccStages];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+
+    dependents_may_launch();
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;            // tile storage starts on a 1024-byte boundary
+    const uint32_t smem_a = tiles, smem_b = tiles + kStages * kBytesA;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                     // 0 issues the MMAs
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), 8); }
+        fence_barrier_init();
+        fence_async_proxy();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                       // both blocks' barriers exist before either is signalled
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM), tiles_n = (p.N + BN - 1) / BN;
+    const int kblocks = (p.K + kBK - 1) / kBK;
+    const int units = tiles_m * tiles_n;
+    const int pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    // unit -> (row tile, weight tile): the row tile runs fastest, so pairs that run together share a weight tile
+
+    if (warp == 0) {
+        if (lane == 0) {
+            wait_for_predecessor();
+            const uint32_t leader_full0 = cluster_addr(smem_u32(&full_bar[0]), 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int u = pair_id; u < units && ok; u += pairs) {
+                const int tm = u % tiles_m, tn = u / tiles_m;
+                const int row_a = tm * 2 * kBM + (int)rank * kBM, row_b = tn * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / kStages) & 1u) ^ 1u, abort_flag, p.error_flag, 301)) { ok = false; break; }
+                    if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * (kBytesA + kBytesB));
+                    const uint32_t bar = leader_full0 + (uint32_t)s * 8u;
+                    tma_load_2d_pair(smem_a + s * kBytesA, &map_a, kb * kBK, row_a, bar);
+                    tma_load_2d_pair(smem_b + s * kBytesB, &map_b, kb * kBK, row_b, bar);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            uint32_t it = 0, acc_it = 0;
+            bool ok = true;
+            for (int u = pair_id; u < units && ok; u += pairs, ++acc_it) {
+                const int as = acc_it % kAccStages;
+                if (!mbar_wait(smem_u32(&acc_empty_bar[as]), ((acc_it / kAccStages) & 1u) ^ 1u, abort_flag, p.error_flag, 302)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + as * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / kStages) & 1u, abort_flag, p.error_flag, 303)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        mma_bf16_pair(tmem_d, smem_desc_sw128(smem_a + s * kBytesA, k * 32), smem_desc_sw128(smem_b + s * kBytesB, k * 32),
+                                      kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit_pair(smem_u32(&empty_bar[s]), 3);
+                }
+                if (ok) mma_commit_pair(smem_u32(&acc_full_bar[as]), 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32 * quarter ..
+        float* outf = (float*)p.out;
+        __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
+        float gate_keep[16];
+        wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
+
+        // What becomes of 16 finished values: row i of x, output features j0 .. j0+15.
+        auto finish = [&](const float (&v)[16], int i, int j0, int c0) {
+            if (p.out_kind == kSwigluBF16) {
+                // Weight rows alternate in runs of 16: gate rows, then the up rows of the same outputs.
+                const int half_n = p.N >> 1;
+                if ((c0 & 16) == 0) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
+                } else if (i < p.M && j0 - 16 < p.N) {
+                    const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
+                    if (j0 + 16 <= p.N && (half_n % 8) == 0) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                                      silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
+                    }
+                }
+            } else if (i < p.M && j0 < p.N) {
+                const size_t o = (size_t)i * p.N + j0;
+                const bool full = j0 + 16 <= p.N;
+                if (p.out_kind == kStoreBF16) {
+                    if (full && (p.N % 8) == 0) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (j0 + c < p.N) outh[o + c] = __float2bfloat16_rn(v[c]);
+                    }
+                } else if (full && (p.N % 4) == 0) {
+                    float4* dst = reinterpret_cast<float4*>(outf + o);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float4 t = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        if (p.out_kind == kAddF32) {
+                            const float4 old = dst[c];
+                            t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+                        }
+                        dst[c] = t;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        if (j0 + c < p.N) {
+                            if (p.out_kind == kAddF32) outf[o + c] += v[c]; else outf[o + c] = v[c];
+                        }
+                }
+            }
+        };
+
+        const uint32_t leader_acc_empty0 = cluster_addr(smem_u32(&acc_empty_bar[0]), 0);
+        uint32_t acc_it = 0;
+        for (int u = pair_id; u < units; u += pairs, ++acc_it) {
+            const int tm = u % tiles_m, tn = u / tiles_m;
+            const int as = acc_it % kAccStages;
+            if (!mbar_wait(smem_u32(&acc_full_bar[as]), (acc_it / kAccStages) & 1u, abort_flag, p.error_flag, 304)) break;
+            tc_fence_after();
+            const int i = tm * 2 * kBM + (int)rank * kBM + quarter * 32 + lane;     // row of x
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r);
+                tmem_ld_wait();
+                float v[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                finish(v, i, tn * BN + c0, c0);
+            }
+            // the accumulator stage is free again: all eight epilogue warps of the pair say so to rank 0
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + (uint32_t)as * 8u);
+        }
+    }
+
+    // Both blocks stay until neither has loads, MMAs or arrivals in flight that touch the other.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix as tiles of [box_rows, 64] with 128-byte swizzle;
+// outside the matrix a tile reads zeros.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_last_error("gemm_tc_pair: the driver does not provide cuTensorMapEncodeTiled");
+        return kNoDriverEntry;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("gemm_tc_pair: cuTensorMapEncodeTiled failed with %d for a [%d, %d] matrix at %p", (int)r, rows, K, base);
+        return kBadShape;
+    }
+    return 0;
+}
+
+// The number of clusters of two that the device runs at once (not every SM has a partner free).
+template <int BN>
+static int resident_pairs(size_t smem) {
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN>, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cached = n;
+    return n;
+}
+
+template <int BN>
+static int launch(const void* x, const void* w, const Params& p, cudaStream_t stream) {
+    constexpr int stages = stages_for<BN>();
+    const size_t smem = (size_t)stages * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 1024;
+    auto kernel = gemm_tc_pair_kernel<BN>;
+    const int pairs_max = resident_pairs<BN>(smem);
+    if (pairs_max <= 0) {
+        set_last_error("gemm_tc_pair: the device runs no cluster of two blocks with %zu bytes of shared memory", smem);
+        return kTooLarge;
+    }
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, x, p.M, p.K, kBM))) return rc;
+    if ((rc = make_map(&mb, w, p.N, p.K, BN / 2))) return rc;
+    const int units = ((p.M + 2 * kBM - 1) / (2 * kBM)) * ((p.N + BN - 1) / BN);
+    const int pairs = units < pairs_max ? units : pairs_max;
+    launch_kernel_clustered(kernel, 2 * pairs, kThreads, smem, 2, stream, ma, mb, p);
+    return CITLALI_LAUNCH_CHECK();
+}
+
+}  // namespace pair
+}  // namespace tc
+}  // namespace citlali
+
+using namespace citlali;
+
+// The tile width the pair kernel would use for this shape and how many pairs the device runs at once
+// (0: it does not run here).
+extern "C" int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs) {
+    (void)M; (void)K;
+    if (bn) *bn = N >= 256 ? 256 : 128;
+    if (pairs) *pairs = N >= 256 ? tc::pair::resident_pairs<256>((size_t)tc::pair::stages_for<256>() * (16384 + 128 * 128) + 1024)
+                                  : tc::pair::resident_pairs<128>((size_t)tc::pair::stages_for<128>() * (16384 + 64 * 128) + 1024);
+    return 0;
+}
+
+// y = x . w^T as citlali_gemm_tc computes it (same `mode` bits, same outputs), on pairs of SMs.
+// For many rows of x; it takes every M, N and K that citlali_gemm_tc takes.
+extern "C" int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                                    int mode, int32_t* error_flag, cudaStream_t stream) {
+    const bool accumulate = (mode & 1) != 0, swiglu = (mode & 2) != 0;
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) {
+        set_last_error("gemm_tc_pair: the inner size %d must be a positive multiple of 8 (rows of 16-byte multiples for TMA)", K);
+        return kBadShape;
+    }
+    if (((uintptr_t)x | (uintptr_t)w) & 15u) {
+        set_last_error("gemm_tc_pair: operands must start on 16-byte boundaries");
+        return kBadAlignment;
+    }
+    if (accumulate && y_dtype != kF32) {
+        set_last_error("gemm_tc_pair: accumulation needs a float32 output");
+        return kBadDType;
+    }
+    if (y_dtype != kF32 && y_dtype != kBF16) {
+        set_last_error("gemm_tc_pair: output dtype code %d is neither float32 nor bfloat16", y_dtype);
+        return kBadDType;
+    }
+    if (swiglu && (accumulate || y_dtype != kBF16 || N % 32 != 0)) {
+        set_last_error("gemm_tc_pair: the gate epilogue needs a bfloat16 output and N a multiple of 32 (N %d)", N);
+        return kBadShape;
+    }
+    tc::pair::Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.error_flag = error_flag;
+    p.out = y;
+    p.out_kind = swiglu ? tc::pair::kSwigluBF16 : accumulate ? tc::pair::kAddF32 : (y_dtype == kF32 ? tc::pair::kStoreF32 : tc::pair::kStoreBF16);
+    return N >= 256 ? tc::pair::launch<256>(x, w, p, stream) : tc::pair::launch<128>(x, w, p, stream);
+}

@@ -265,6 +265,32 @@ def gemm_tc_plan(M: int, N: int, K: int, device, force_splits: int = 0) -> dict:
     return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value}
 
 
+def gemm_tc_pair_plan(M: int, N: int, K: int) -> dict:
+    """The pair kernel's tile width for this shape and how many clusters of two the device runs at once."""
+    bn, pairs = ctypes.c_int(), ctypes.c_int()
+    lib().citlali_gemm_tc_pair_plan(_i(M), _i(N), _i(K), ctypes.byref(bn), ctypes.byref(pairs))
+    return {"bn": bn.value, "pairs": pairs.value}
+
+
+def gemm_tc_set_pair_rows(rows: int) -> None:
+    """From ``rows`` rows of ``x`` on, ``gemm_tc`` runs on pairs of SMs (0: never)."""
+    lib().citlali_gemm_tc_set_pair_rows(_i(rows))
+
+
+def gemm_tc_pair(x, w, y, accumulate=False, error_flag=None, swiglu=False):
+    """``gemm_tc`` on pairs of SMs (tcgen05.mma with cta_group::2), whatever the number of rows."""
+    _need_cuda(x, w, y, error_flag)
+    M, K = x.shape
+    N = w.shape[0]
+    require(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and w.shape[1] == K
+            and x.is_contiguous() and w.is_contiguous(),
+            "gemm_tc_pair: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
+    require(y.shape == (M, N // 2 if swiglu else N), "gemm_tc_pair: the output's shape does not fit")
+    mode = (1 if accumulate else 0) | (2 if swiglu else 0)
+    _check(lib().citlali_gemm_tc_pair(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode),
+                                      _ptr(error_flag), _stream()), "gemm_tc_pair")
+
+
 def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
     """One scratch buffer per device and purpose (split-context attention partials, argmax segments);
     it only grows.  Kernels on one stream use it one after another."""

@@ -428,6 +428,52 @@ def test_gemm_tc_gate_epilogue(M, inter, K):
         ops.gemm_tc(x.to(DEV), packed[:2 * inter - 16].contiguous().to(DEV), torch.empty(M, inter - 8, dtype=torch.bfloat16, device=DEV), swiglu=True)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (130, 144, 72), (1000, 1000, 512), (2048, 4096, 1024),
+                                   (513, 96, 4096)])
+def test_gemm_tc_on_pairs_of_sms(M, N, K):
+    """The product with cta_group::2 (two blocks of a cluster on one [256 x BN] tile), every output kind,
+    sizes that are no multiple of any tile; and the same through gemm_tc's own dispatch."""
+    if ops.gemm_tc_pair_plan(M, N, K)["pairs"] == 0:
+        pytest.skip("this device runs no cluster of two blocks of that size")
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16); w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    scale = float(want.abs().max())
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    xd, wd = x.to(DEV), w.to(DEV)
+    y32 = torch.full((M, N), 7.0, device=DEV)
+    ops.gemm_tc_pair(xd, wd, y32, error_flag=flag)
+    err = float((y32.double().cpu() - want).abs().max())
+    assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)), f"float32 out: |diff| {err:.3e} of {scale:.3e}"
+    y16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc_pair(xd, wd, y16, error_flag=flag)
+    close(y16, want, torch.bfloat16)
+    base = torch.randn(M, N, generator=g)
+    acc = base.to(DEV).clone()
+    ops.gemm_tc_pair(xd, wd, acc, accumulate=True, error_flag=flag)
+    err = float((acc.double().cpu() - (base.double() + want)).abs().max())
+    assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)) + 1e-6
+    if N % 32 == 0:
+        wg, wu = w[:N // 2] * 0.2, w[N // 2:] * 0.2
+        wg, wu = wg.to(torch.bfloat16), wu.to(torch.bfloat16)
+        packed = torch.stack([wg.view(-1, 16, K), wu.view(-1, 16, K)], dim=1).reshape(N, K).contiguous()
+        act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc_pair(xd, packed.to(DEV), act, swiglu=True, error_flag=flag)
+        close(act, plain.swiglu(x.double() @ wg.double().t(), x.double() @ wu.double().t()), torch.bfloat16)
+    # the one-block kernel and the pair kernel add the K blocks in the same order
+    one = torch.empty(M, N, device=DEV)
+    ops.gemm_tc(xd, wd, one, error_flag=flag)
+    try:
+        ops.gemm_tc_set_pair_rows(128)
+        two = torch.empty(M, N, device=DEV)
+        ops.gemm_tc(xd, wd, two, error_flag=flag)
+    finally:
+        ops.gemm_tc_set_pair_rows(0)
+    assert torch.equal(two, y32)
+    assert float((one - two).abs().max()) <= 2e-6 * scale
+    assert flag.tolist() == [0, 0, 0, 0]
+
+
 def test_gemm_tc_split_k_sums_in_one_order():
     """K split over a cluster of blocks: the same bits every time, and for every forced split the sum is right."""
     g = torch.Generator().manual_seed(4)
