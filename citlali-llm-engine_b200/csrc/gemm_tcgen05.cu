@@ -35,8 +35,13 @@
 namespace citlali {
 namespace tc {
 
+__device__ __forceinline__ int warp_of(unsigned thread) { return (int)(thread >> 5); }
+
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
-constexpr int kThreads = 192;
+// two role warps and the epilogue warps: four when the weights are the 128-row operand (decoding), eight for
+// prompts, where a tile's epilogue must not outlast the next tile's main loop
+__host__ __device__ constexpr int epilogue_warps(bool swapped) { return swapped ? 4 : 8; }
+__host__ __device__ constexpr int threads_for(bool swapped) { return 64 + 32 * epilogue_warps(swapped); }
 constexpr int kMaxSplits = 8;       // a cluster's portable size
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
@@ -55,8 +60,8 @@ struct GemmParams {
 template <int BN>
 constexpr int stages_for(bool swapped) {
     // swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
-    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of 192 KB
-    return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 224 ? 5 : 4);
+    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of about 200 KB and 20 KB for the epilogue warps
+    return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
 __device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
@@ -69,7 +74,7 @@ __device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
 }
 
 template <int BN, bool kSwapped>
-__global__ void __launch_bounds__(kThreads, (kSwapped && BN <= 64) ? 2 : 1)
+__global__ void __launch_bounds__(threads_for(kSwapped), (kSwapped && BN <= 64) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int kStages = stages_for<BN>(kSwapped);
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
@@ -91,13 +96,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // tile.  Behind the ring for narrow tiles; over the ring for wide ones, which then need a cluster
     // barrier between the last MMA of every block and the first partial sent.
     constexpr bool kRecvInRing = BN >= 64;
+    // normal form: behind the ring, an area for each epilogue warp to turn its values round in (tc_common.cuh)
+    const uint32_t epilogue_stage = tiles + kStages * (kBytesA + kBytesB) + (uint32_t)((warp_of(threadIdx.x) - 2) & 7) * kEpilogueStageBytes;
     const uint32_t recv = kRecvInRing ? tiles : tiles + kStages * (kBytesA + kBytesB);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         abort_word = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), 4); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), epilogue_warps(kSwapped)); }
         fence_barrier_init();
         fence_async_proxy();
     }
@@ -211,6 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         float* outf = (float*)p.out;
         __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
         float gate_keep[16];
+        const uint64_t out_policy = l2_evict_first_policy();
         wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
 
         // What becomes of 16 finished values: row i of the 128-row operand, rows j0 .. j0+15 of the other.
@@ -232,6 +240,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     // this thread holds 16 consecutive columns: a gate run on even chunks, its up run on odd ones
 #pragma unroll
                     for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
+                } else if (j0 + 16 <= p.N && (half_n % 8) == 0) {
+                    // whole run: the warp writes its 32 rows x 16 outputs with full sectors
+                    uint32_t w[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                                  silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                        w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    const int row0 = i - lane;
+                    warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * half_n + ((j0 - 16) >> 1), (size_t)half_n, p.M - row0, lane, out_policy);
                 } else if (i < p.M && j0 - 16 < p.N) {
                     const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
                     if (j0 + 16 <= p.N && (half_n % 8) == 0) {
@@ -265,6 +284,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     }
                 }
+            } else if (p.out_kind == kStoreBF16 && j0 + 16 <= p.N && (p.N % 8) == 0) {
+                // i is a row m of x, j an output feature n; whole chunk: the warp writes 32 rows x 16 with full sectors
+                uint32_t w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                const int row0 = i - lane;
+                warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, out_policy);
+            } else if (p.out_kind != kStoreBF16 && j0 + 16 <= p.N && (p.N % 4) == 0) {
+                const int row0 = i - lane;
+                warp_rows_out_f32(epilogue_stage, v, outf + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, p.out_kind == kAddF32, out_policy);
             } else if (i < p.M && j0 < p.N) {
                 // i is a row m of x, j an output feature n: this thread holds 16 consecutive n
                 const size_t o = (size_t)i * p.N + j0;
@@ -326,8 +358,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int units_per_owner = (BN + p.splits - 1) / p.splits;
             const bool pow2 = (p.splits & (p.splits - 1)) == 0;     // the plan's splits are; a forced split may not be
             const int shift = 31 - __clz(p.splits);
+            if (!kSwapped) {
+                // prompts: the columns go in pairs of 16-column chunks (a gate run and its up run), the pairs
+                // alternately to the two warps that share these 32 tensor-memory lanes; both chunks of a pair
+                // are read before either is worked on
+                const int half = (warp - 2) >> 2;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = half * 32; c0 < BN; c0 += 64) {
+                    const bool two = c0 + 16 < BN;
+                    uint32_t r0[16], r1[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r0);
+                    if (two) tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0 + 16, r1);
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r0[c]);
+                    finish(v, i, tb * BN + c0, c0);
+                    if (two) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r1[c]);
+                        finish(v, i, tb * BN + c0 + 16, c0 + 16);
+                    }
+                }
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < (kSwapped ? BN : 0); c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r);
                 tmem_ld_wait();
@@ -453,7 +508,7 @@ struct Plan {
 
 // The plan is a function of the shape alone.  Swapped up to 128 rows of x; the split aims at
 // two blocks on every SM and keeps at least four K blocks per block.
-static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
+static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, bool gate_runs = false) {
     Plan pl;
     pl.swapped = M <= 128;
     if (pl.swapped) {
@@ -482,6 +537,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
             const int tiles_m = (M + kBM - 1) / kBM;
             long best = -1;
             for (int bn : {256, 240, 224, 208, 192}) {
+                if (gate_runs && bn % 32 != 0) continue;      // a tile must hold whole pairs of gate and up runs
                 const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
                 const long cost = ((tiles + sm_count - 1) / sm_count) * (2000 + 3 * bn);
                 if (best < 0 || cost < best) { best = cost; pl.bn = bn; }
@@ -494,7 +550,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0) {
 template <int BN, bool kSwapped>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
     constexpr int stages = stages_for<BN>(kSwapped);
-    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + (kSwapped && BN < 64 ? BN * 512 + 4096 : 0) + 1024;      // ring, split-K receive area behind it, alignment
+    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + (kSwapped ? (BN < 64 ? BN * 512 + 4096 : 0) : 8 * kEpilogueStageBytes) + 1024;      // ring, split-K receive area behind it, alignment
     auto kernel = gemm_tc_kernel<BN, kSwapped>;
     static bool configured = false;
     if (!configured) {
@@ -507,7 +563,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     const int per_sm = (kSwapped && BN <= 64) ? 2 : 1;
     // split K: one block per (tile, split), the splits of a tile being one cluster; else a persistent grid
     const int grid = p.splits > 1 ? units : (units < sm_count * per_sm ? units : sm_count * per_sm);
-    launch_kernel_clustered(kernel, grid, kThreads, smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
+    launch_kernel_clustered(kernel, grid, threads_for(kSwapped), smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -566,7 +622,7 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
         return kBadShape;
     }
     if (sm_count <= 0) sm_count = 148;
-    const Plan pl = make_plan(M, N, K, sm_count, force_splits);
+    const Plan pl = make_plan(M, N, K, sm_count, force_splits, swiglu);
     if (!pl.swapped && g_pair_rows > 0 && M >= g_pair_rows) {
         int bn = 0, pairs = 0;
         citlali_gemm_tc_pair_plan(M, N, K, &bn, &pairs);

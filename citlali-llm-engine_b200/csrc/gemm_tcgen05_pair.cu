@@ -11,7 +11,9 @@
 //                     the full barrier of the block with rank 0; neither load is multicast.
 //   warp 1:           allocates tensor memory (both blocks, together); in the block with rank 0 one
 //                     lane issues the MMAs; tcgen05.commit arrives on the barriers of both blocks.
-//   warps 2-5:        epilogue of this block's 128 rows; the accumulator stage is handed back on a
+//   warps 2-9:        epilogue of this block's 128 rows (two warps share 32 tensor-memory lanes and take
+//                     alternate pairs of 16-column chunks; values leave through shared memory so that every
+//                     store covers whole sectors); the accumulator stage is handed back on a
 //                     barrier of the block with rank 0 on which the warps of both blocks arrive.
 // Every wait on an mbarrier gives up after a time limit, raises the error word and makes the block
 // leave through the normal exit (cluster barrier, tensor memory freed).
@@ -24,7 +26,8 @@ namespace tc {
 namespace pair {
 
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kTmemCols = 512;
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
@@ -59,13 +62,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tiles = (raw + 1023u) & ~1023u;            // tile storage starts on a 1024-byte boundary
     const uint32_t smem_a = tiles, smem_b = tiles + kStages * kBytesA;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t epilogue_stage = tiles + kStages * (kBytesA + kBytesB) + (uint32_t)((warp - 2) & 7) * kEpilogueStageBytes;
     const uint32_t rank = cluster_rank();                     // 0 issues the MMAs
     const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
         abort_word = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), 8); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), 2 * kEpilogueWarps); }
         fence_barrier_init();
         fence_async_proxy();
     }
@@ -134,6 +138,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         float* outf = (float*)p.out;
         __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
         float gate_keep[16];
+        const uint64_t out_policy = l2_evict_first_policy();
         wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
 
         // What becomes of 16 finished values: row i of x, output features j0 .. j0+15.
@@ -144,6 +149,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if ((c0 & 16) == 0) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
+                } else if (j0 + 16 <= p.N && (half_n % 8) == 0) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                                  silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                        w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    const int row0 = i - lane;
+                    warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * half_n + ((j0 - 16) >> 1), (size_t)half_n, p.M - row0, lane, out_policy);
                 } else if (i < p.M && j0 - 16 < p.N) {
                     const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
                     if (j0 + 16 <= p.N && (half_n % 8) == 0) {
@@ -163,6 +178,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
                     }
                 }
+            } else if (p.out_kind == kStoreBF16 && j0 + 16 <= p.N && (p.N % 8) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                const int row0 = i - lane;
+                warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, out_policy);
+            } else if (p.out_kind != kStoreBF16 && j0 + 16 <= p.N && (p.N % 4) == 0) {
+                const int row0 = i - lane;
+                warp_rows_out_f32(epilogue_stage, v, outf + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, p.out_kind == kAddF32, out_policy);
             } else if (i < p.M && j0 < p.N) {
                 const size_t o = (size_t)i * p.N + j0;
                 const bool full = j0 + 16 <= p.N;
@@ -211,15 +238,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!mbar_wait(smem_u32(&acc_full_bar[as]), (acc_it / kAccStages) & 1u, abort_flag, p.error_flag, 304)) break;
             tc_fence_after();
             const int i = tm * 2 * kBM + (int)rank * kBM + quarter * 32 + lane;     // row of x
+            const int half = (warp - 2) >> 2;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r);
+            for (int c0 = half * 32; c0 < BN; c0 += 64) {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r0);
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0 + 16, r1);
                 tmem_ld_wait();
                 float v[16];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r0[c]);
                 finish(v, i, tn * BN + c0, c0);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r1[c]);
+                finish(v, i, tn * BN + c0 + 16, c0 + 16);
             }
             // the accumulator stage is free again: all eight epilogue warps of the pair say so to rank 0
             tc_fence_before();
@@ -308,7 +340,7 @@ static int resident_pairs(size_t smem) {
 template <int BN>
 static int launch(const void* x, const void* w, const Params& p, cudaStream_t stream) {
     constexpr int stages = stages_for<BN>();
-    const size_t smem = (size_t)stages * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 1024;
+    const size_t smem = (size_t)stages * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + kEpilogueWarps * kEpilogueStageBytes + 1024;
     auto kernel = gemm_tc_pair_kernel<BN>;
     const int pairs_max = resident_pairs<BN>(smem);
     if (pairs_max <= 0) {
@@ -336,8 +368,8 @@ using namespace citlali;
 extern "C" int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs) {
     (void)M; (void)K;
     if (bn) *bn = N >= 256 ? 256 : 128;
-    if (pairs) *pairs = N >= 256 ? tc::pair::resident_pairs<256>((size_t)tc::pair::stages_for<256>() * (16384 + 128 * 128) + 1024)
-                                  : tc::pair::resident_pairs<128>((size_t)tc::pair::stages_for<128>() * (16384 + 64 * 128) + 1024);
+    if (pairs) *pairs = N >= 256 ? tc::pair::resident_pairs<256>((size_t)tc::pair::stages_for<256>() * (16384 + 128 * 128) + tc::pair::kEpilogueWarps * tc::kEpilogueStageBytes + 1024)
+                                  : tc::pair::resident_pairs<128>((size_t)tc::pair::stages_for<128>() * (16384 + 64 * 128) + tc::pair::kEpilogueWarps * tc::kEpilogueStageBytes + 1024);
     return 0;
 }
 

@@ -186,5 +186,72 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t mask) {
                  ::"r"(bar), "h"(mask) : "memory");
 }
 
+// ---- epilogue: a warp's 32 rows x 16 values, written with full sectors ------------------------
+// A thread holds 16 consecutive outputs of ITS row (lane = row), so a plain store touches 32 rows with 16
+// bytes each.  Here the warp turns the values round in a private shared-memory area of kEpilogueStageBytes
+// and writes them so that every instruction covers whole 32-byte sectors: 8 rows x 64 bytes (float) or
+// 16 rows x 32 bytes (bfloat16).  `out` points at row `row0`, column j0 of the output; rows from `rows_left`
+// on do not exist.
+constexpr uint32_t kEpilogueStageBytes = 32 * 20 * 4;
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+// The outputs stream out once: they are marked to leave L2 first, so that they do not push out the
+// operand tiles that other blocks are about to read again.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void red_add_v4(float* addr, uint4 v, uint64_t policy) {
+    asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void st_global_v4_hint(void* addr, uint4 v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
+}
+// 16 floats a row: stored, or added to what is there (one add per element, by one thread: the same sum
+// as a load, an add and a store).
+__device__ __forceinline__ void warp_rows_out_f32(uint32_t stage, const float (&v)[16], float* out, size_t pitch, int rows_left,
+                                                  int lane, bool add, uint64_t policy) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        st_shared_v4(stage + (uint32_t)(lane * 20 + 4 * k) * 4u, __float_as_uint(v[4 * k]), __float_as_uint(v[4 * k + 1]),
+                     __float_as_uint(v[4 * k + 2]), __float_as_uint(v[4 * k + 3]));
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + (lane >> 2), cw = (lane & 3) * 4;
+        const uint4 t = ld_shared_v4(stage + (uint32_t)(r * 20 + cw) * 4u);
+        if (r < rows_left) {
+            float* dst = out + (size_t)r * pitch + cw;
+            if (add) red_add_v4(dst, t, policy); else st_global_v4_hint(dst, t, policy);
+        }
+    }
+    __syncwarp();
+}
+// 16 bfloat16 a row, given as 8 words of two.
+__device__ __forceinline__ void warp_rows_out_bf16(uint32_t stage, const uint32_t (&w)[8], __nv_bfloat16* out, size_t pitch, int rows_left,
+                                                   int lane, uint64_t policy) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+        st_shared_v4(stage + (uint32_t)(lane * 12 + 4 * k) * 4u, w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int r = it * 16 + (lane >> 1), cw = (lane & 1) * 4;
+        const uint4 t = ld_shared_v4(stage + (uint32_t)(r * 12 + cw) * 4u);
+        if (r < rows_left) st_global_v4_hint(out + (size_t)r * pitch + cw * 2, t, policy);
+    }
+    __syncwarp();
+}
+
 }  // namespace tc
 }  // namespace citlali

@@ -413,7 +413,8 @@ def test_attention_prefill_flash(nq, nkv, d, window):
 
 
 @pytest.mark.parametrize("M,inter,K", [(1, 192, 64), (8, 12288, 512), (70, 160, 96), (128, 48, 64), (129, 64, 128),
-                                       (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024)])
+                                       (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024), (2048, 2048, 128),
+                                       (1200, 1200, 64)])
 def test_gemm_tc_gate_epilogue(M, inter, K):
     """silu(gate) * up straight from the product's epilogue, in both forms and with K split."""
     g = torch.Generator().manual_seed(M + inter)
