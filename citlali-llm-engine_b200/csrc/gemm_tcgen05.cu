@@ -35,8 +35,6 @@
 namespace citlali {
 namespace tc {
 
-__device__ __forceinline__ int warp_of(unsigned thread) { return (int)(thread >> 5); }
-
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
 // two role warps and the epilogue warps: four when the weights are the 128-row operand (decoding), eight for
 // prompts, where a tile's epilogue must not outlast the next tile's main loop
@@ -59,8 +57,9 @@ struct GemmParams {
 
 template <int BN>
 constexpr int stages_for(bool swapped) {
-    // swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
-    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of about 200 KB and 20 KB for the epilogue warps
+    // Swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
+    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of
+    // about 200 KB, and 20 KB behind the ring for the epilogue warps.
     return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
@@ -96,10 +95,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // tile.  Behind the ring for narrow tiles; over the ring for wide ones, which then need a cluster
     // barrier between the last MMA of every block and the first partial sent.
     constexpr bool kRecvInRing = BN >= 64;
-    // normal form: behind the ring, an area for each epilogue warp to turn its values round in (tc_common.cuh)
-    const uint32_t epilogue_stage = tiles + kStages * (kBytesA + kBytesB) + (uint32_t)((warp_of(threadIdx.x) - 2) & 7) * kEpilogueStageBytes;
-    const uint32_t recv = kRecvInRing ? tiles : tiles + kStages * (kBytesA + kBytesB);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t behind_ring = tiles + kStages * (kBytesA + kBytesB);
+    const uint32_t recv = kRecvInRing ? tiles : behind_ring;
+    // normal form: an area for each epilogue warp to turn its values round in (tc_common.cuh)
+    const uint32_t epilogue_stage = behind_ring + (uint32_t)((warp - 2) & 7) * kEpilogueStageBytes;
 
     if (threadIdx.x == 0) {
         abort_word = 0;
@@ -122,11 +122,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb_per_split = (kblocks + p.splits - 1) / p.splits;
     const int units = tiles_a * tiles_b * p.splits;
 
-    // unit -> (a tile, b tile, split).  Normal: the x tile index runs fastest, so blocks that run
-    // together share a weight tile.  Swapped: the split runs fastest, then the weight tile.
+    // unit -> (a tile, b tile, split): the split runs fastest (the blocks of a cluster), then the tile of the
+    // 128-row operand.  Normal form (no split): blocks that run together share a weight tile.
     auto decode = [&](int u, int& ta, int& tb, int& sp) {
-        if (kSwapped) { sp = u % p.splits; u /= p.splits; ta = u % tiles_a; tb = u / tiles_a; }
-        else { sp = u % p.splits; u /= p.splits; ta = u % tiles_a; tb = u / tiles_a; }
+        sp = u % p.splits; u /= p.splits; ta = u % tiles_a; tb = u / tiles_a;
     };
 
     if (warp == 0) {
