@@ -36,10 +36,11 @@ namespace citlali {
 namespace tc {
 
 constexpr int kBM = 128, kBK = 64, kAccStages = 2;
-// two role warps and the epilogue warps: four when the weights are the 128-row operand (decoding), eight for
-// prompts, where a tile's epilogue must not outlast the next tile's main loop
-__host__ __device__ constexpr int epilogue_warps(bool swapped) { return swapped ? 4 : 8; }
-__host__ __device__ constexpr int threads_for(bool swapped) { return 64 + 32 * epilogue_warps(swapped); }
+// two role warps and the epilogue warps: eight for prompts, where a tile's epilogue must not outlast the next
+// tile's main loop, and for 64 and more rows of x with the weights as the 128-row operand (a block's only
+// epilogue is not hidden by anything there); four for fewer rows
+__host__ __device__ constexpr int epilogue_warps(bool swapped, int bn) { return swapped && bn < 64 ? 4 : 8; }
+__host__ __device__ constexpr int threads_for(bool swapped, int bn) { return 64 + 32 * epilogue_warps(swapped, bn); }
 constexpr int kMaxSplits = 8;       // a cluster's portable size
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
@@ -60,7 +61,7 @@ constexpr int stages_for(bool swapped) {
     // Swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
     // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of
     // about 200 KB, and 20 KB behind the ring for the epilogue warps.
-    return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 64 ? 4 : 6) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
+    return swapped ? (BN <= 16 ? 5 : BN <= 64 ? 4 : 3) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
 __device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
@@ -73,7 +74,7 @@ __device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
 }
 
 template <int BN, bool kSwapped>
-__global__ void __launch_bounds__(threads_for(kSwapped), (kSwapped && BN <= 64) ? 2 : 1)
+__global__ void __launch_bounds__(threads_for(kSwapped, BN), kSwapped ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int kStages = stages_for<BN>(kSwapped);
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
@@ -104,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         abort_word = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), epilogue_warps(kSwapped)); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), epilogue_warps(kSwapped, BN)); }
         fence_barrier_init();
         fence_async_proxy();
     }
@@ -380,8 +381,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
+            constexpr int kWarpsPerQuarter = epilogue_warps(kSwapped, BN) / 4;
 #pragma unroll 1
-            for (int c0 = 0; c0 < (kSwapped ? BN : 0); c0 += 16) {
+            for (int c0 = kSwapped ? ((warp - 2) >> 2) * 16 : BN; c0 < BN; c0 += 16 * kWarpsPerQuarter) {
                 uint32_t r[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + c0, r);
                 tmem_ld_wait();
@@ -422,7 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             float* outf = (float*)p.out;
             __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
 #pragma unroll 1
-            for (int ul = warp - 2; ul < units_per_owner; ul += 4) {
+            for (int ul = warp - 2; ul < units_per_owner; ul += epilogue_warps(kSwapped, BN)) {
                 const int unit = ul * p.splits + sp;
                 if (unit >= BN) break;
                 const int m0 = tb * BN + (unit >> 2) * 4, n = ta * kBM + (unit & 3) * 32 + lane;
@@ -514,7 +516,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, b
         pl.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         const int tiles = (N + kBM - 1) / kBM;
         const int kblocks = (K + kBK - 1) / kBK;
-        const int slots = sm_count * (pl.bn <= 64 ? 2 : 1);
+        const int slots = sm_count * 2;                      // two blocks per SM in this form
         int s = slots / tiles;
         if (s > kblocks / 4) s = kblocks / 4;
         if (s > kMaxSplits) s = kMaxSplits;
@@ -559,10 +561,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     }
     const int tiles_a = (p.rows_a + kBM - 1) / kBM, tiles_b = (p.rows_b + BN - 1) / BN;
     const int units = tiles_a * tiles_b * p.splits;
-    const int per_sm = (kSwapped && BN <= 64) ? 2 : 1;
+    const int per_sm = kSwapped ? 2 : 1;
     // split K: one block per (tile, split), the splits of a tile being one cluster; else a persistent grid
     const int grid = p.splits > 1 ? units : (units < sm_count * per_sm ? units : sm_count * per_sm);
-    launch_kernel_clustered(kernel, grid, threads_for(kSwapped), smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
+    launch_kernel_clustered(kernel, grid, threads_for(kSwapped, BN), smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
     return CITLALI_LAUNCH_CHECK();
 }
 
