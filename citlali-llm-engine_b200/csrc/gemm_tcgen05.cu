@@ -45,7 +45,8 @@ constexpr int kMaxSplits = 8;       // a cluster's portable size
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// silu(g) * u with the fast exponential and the approximate division (a few ulp, before rounding to bfloat16)
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct GemmParams {
     void* out;             // [M, N] (or the partials' workspace [splits, M, N])

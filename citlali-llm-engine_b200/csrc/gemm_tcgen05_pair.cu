@@ -32,7 +32,8 @@ constexpr uint32_t kTmemCols = 512;
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// silu(g) * u with the fast exponential and the approximate division (a few ulp, before rounding to bfloat16)
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct Params {
     void* out;
