@@ -49,7 +49,7 @@ enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct GemmParams {
-    void* out;             // [M, N] (or the partials' workspace [splits, M, N])
+    void* out;             // [M, N] ([M, N / 2] under the gate epilogue)
     int out_kind;
     int M, N, K;           // the product's logical shape: y[M, N] = x[M, K] w[N, K]^T
     int rows_a, rows_b;    // rows of the 128-row operand and of the BN-row operand
