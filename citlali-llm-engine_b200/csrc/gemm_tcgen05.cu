@@ -42,6 +42,7 @@ constexpr int kBM = 128, kBK = 64, kAccStages = 2;
 __host__ __device__ constexpr int epilogue_warps(bool swapped, int bn) { return swapped && bn < 64 ? 4 : 8; }
 __host__ __device__ constexpr int threads_for(bool swapped, int bn) { return 64 + 32 * epilogue_warps(swapped, bn); }
 constexpr int kMaxSplits = 8;       // a cluster's portable size
+constexpr int kMaxSwappedRows = 256;
 
 enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
 
@@ -59,10 +60,11 @@ struct GemmParams {
 
 template <int BN>
 constexpr int stages_for(bool swapped) {
-    // Swapped (decoding): two blocks per SM of about 100 KB each; up to 32 rows of x the split-K receive
-    // area (BN x 512 bytes) lies behind the ring, wider tiles reuse the ring for it.  Normal: one block of
+    // Swapped (few rows of x): two blocks per SM of about 100 KB each (one of 192 KB for tiles of 256 rows of
+    // x); up to 32 rows of x the split-K receive area (BN x 512 bytes) lies behind the ring, wider tiles
+    // reuse the ring for it.  Normal: one block of
     // about 200 KB, and 20 KB behind the ring for the epilogue warps.
-    return swapped ? (BN <= 16 ? 5 : BN <= 64 ? 4 : 3) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
+    return swapped ? (BN <= 16 ? 5 : BN <= 64 ? 4 : BN <= 128 ? 3 : 4) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
 __device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
@@ -75,7 +77,7 @@ __device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
 }
 
 template <int BN, bool kSwapped>
-__global__ void __launch_bounds__(threads_for(kSwapped, BN), kSwapped ? 2 : 1)
+__global__ void __launch_bounds__(threads_for(kSwapped, BN), (kSwapped && BN <= 128) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int kStages = stages_for<BN>(kSwapped);
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
@@ -508,16 +510,36 @@ struct Plan {
     int splits;
 };
 
-// The plan is a function of the shape alone.  Swapped up to 128 rows of x; the split aims at
-// two blocks on every SM and keeps at least four K blocks per block.
+// The plan is a function of the shape alone.
+// Normal form: the grid runs in waves of one block per SM; the narrow tile's width is chosen so that the last
+// wave is as full as possible (measured at 2,048 rows, a tile's time hardly depends on its width: about
+// 20 + 0.03 x width microseconds at K = 4096).
+// Swapped form: up to 128 rows of x always; up to kMaxSwappedRows rows (one tile of 256 rows of x) when the
+// normal form would leave SMs without a tile, i.e. against a narrow weight matrix: a tile's K loop of 26 us
+// would then bound the product, while here every weight tile is streamed once and K is split over the SMs.
+// The split aims at a block (two for narrow tiles) on every SM and keeps at least four K blocks per block.
 static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, bool gate_runs = false) {
     Plan pl;
-    pl.swapped = M <= 128;
-    if (pl.swapped) {
-        pl.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    pl.swapped = false;
+    pl.bn = 128;
+    pl.splits = 1;
+    long normal_tiles = (long)((M + kBM - 1) / kBM) * ((N + 127) / 128);
+    if (N >= 192) {
+        const int tiles_m = (M + kBM - 1) / kBM;
+        long best = -1;
+        for (int bn : {256, 240, 224, 208, 192}) {
+            if (gate_runs && bn % 32 != 0) continue;      // a tile must hold whole pairs of gate and up runs
+            const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+            const long cost = ((tiles + sm_count - 1) / sm_count) * (2000 + 3 * bn);
+            if (best < 0 || cost < best) { best = cost; pl.bn = bn; normal_tiles = tiles; }
+        }
+    }
+    if (M <= 128 || (M <= kMaxSwappedRows && normal_tiles < sm_count)) {
+        pl.swapped = true;
+        pl.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
         const int tiles = (N + kBM - 1) / kBM;
         const int kblocks = (K + kBK - 1) / kBK;
-        const int slots = sm_count * 2;                      // two blocks per SM in this form
+        const int slots = sm_count * (pl.bn <= 128 ? 2 : 1);
         int s = slots / tiles;
         if (s > kblocks / 4) s = kblocks / 4;
         if (s > kMaxSplits) s = kMaxSplits;
@@ -529,22 +551,6 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, b
         if (s > kblocks) s = kblocks;
         if (s < 1) s = 1;
         pl.splits = s;
-    } else {
-        // The grid runs in waves of one block per SM; the narrow tile's width is chosen so that the last
-        // wave is as full as possible.  Measured at 2,048 rows, a tile's time hardly depends on its width
-        // (operand traffic from L2 bounds it, not the MMAs): about 20 + 0.03 x width microseconds at K = 4096.
-        pl.bn = 128;
-        pl.splits = 1;
-        if (N >= 192) {
-            const int tiles_m = (M + kBM - 1) / kBM;
-            long best = -1;
-            for (int bn : {256, 240, 224, 208, 192}) {
-                if (gate_runs && bn % 32 != 0) continue;      // a tile must hold whole pairs of gate and up runs
-                const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
-                const long cost = ((tiles + sm_count - 1) / sm_count) * (2000 + 3 * bn);
-                if (best < 0 || cost < best) { best = cost; pl.bn = bn; }
-            }
-        }
     }
     return pl;
 }
@@ -562,7 +568,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
     }
     const int tiles_a = (p.rows_a + kBM - 1) / kBM, tiles_b = (p.rows_b + BN - 1) / BN;
     const int units = tiles_a * tiles_b * p.splits;
-    const int per_sm = kSwapped ? 2 : 1;
+    const int per_sm = (kSwapped && BN <= 128) ? 2 : 1;
     // split K: one block per (tile, split), the splits of a tile being one cluster; else a persistent grid
     const int grid = p.splits > 1 ? units : (units < sm_count * per_sm ? units : sm_count * per_sm);
     launch_kernel_clustered(kernel, grid, threads_for(kSwapped, BN), smem, p.splits > 1 ? p.splits : 1, stream, ma, mb, p);
@@ -647,7 +653,8 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
             case 16: rc = launch<16, true>(ma, mb, p, sm_count, stream); break;
             case 32: rc = launch<32, true>(ma, mb, p, sm_count, stream); break;
             case 64: rc = launch<64, true>(ma, mb, p, sm_count, stream); break;
-            default: rc = launch<128, true>(ma, mb, p, sm_count, stream); break;
+            case 128: rc = launch<128, true>(ma, mb, p, sm_count, stream); break;
+            default: rc = launch<256, true>(ma, mb, p, sm_count, stream); break;
         }
     } else {
         if ((rc = make_map(&ma, x, M, K, kBM))) return rc;

@@ -291,7 +291,8 @@ def test_sample_rows_follows_the_cdf(V):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 192, 64), (17, 1000, 96), (33, 130, 200), (64, 4096, 512),
                                    (100, 24, 4096), (128, 256, 512), (129, 256, 128), (300, 520, 200),
-                                   (1000, 96, 72), (2048, 512, 1024), (1, 4096, 12288)])
+                                   (1000, 96, 72), (2048, 512, 1024), (1, 4096, 12288), (256, 4096, 4096), (200, 1000, 12288),
+                                   (512, 4096, 2048)])
 def test_gemm_tc(M, N, K):
     """The tensor-core product in both of its forms (weights on the wide side for few rows, rows
     on the wide side for many), with sizes that are no multiple of any tile, K that is split and
@@ -317,7 +318,7 @@ def test_gemm_tc(M, N, K):
     assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)) + 1e-6
     assert flag.tolist() == [0, 0, 0, 0]
     plan = ops.gemm_tc_plan(M, N, K, DEV)
-    assert plan["swapped"] == (M <= 128)
+    assert plan["swapped"] or M > 128          # few rows: the weights are the 128-row operand
 
 
 def test_gemm_tc_rows_do_not_depend_on_the_batch():
@@ -414,7 +415,7 @@ def test_attention_prefill_flash(nq, nkv, d, window):
 
 @pytest.mark.parametrize("M,inter,K", [(1, 192, 64), (8, 12288, 512), (70, 160, 96), (128, 48, 64), (129, 64, 128),
                                        (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024), (2048, 2048, 128),
-                                       (1200, 1200, 64)])
+                                       (1200, 1200, 64), (256, 1024, 2048), (300, 2048, 4096)])
 def test_gemm_tc_gate_epilogue(M, inter, K):
     """silu(gate) * up straight from the product's epilogue, in both forms and with K split."""
     g = torch.Generator().manual_seed(M + inter)
