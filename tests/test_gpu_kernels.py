@@ -378,6 +378,33 @@ def test_attention_decode_split_over_the_context(nq, nkv, d, page, window):
         assert (out[-1].view(nq, d)[0].double().cpu() - v[-1][7, 0]).abs().max() < 0.1
 
 
+def test_attention_decode_one_long_sequence():
+    """One sequence of 8,400 tokens in a cache laid out for more than 8,192: the blocks of a head group are a
+    cluster of sixteen.  A far key takes nearly all the weight of one head; with a window only its keys count."""
+    g = torch.Generator().manual_seed(11)
+    dtype, page, nq, nkv, d, n = torch.bfloat16, 64, 8, 2, 128, 8400
+    k = [torch.randn(n, nkv, d, generator=g).to(dtype).double()]
+    v = [torch.randn(n, nkv, d, generator=g).to(dtype).double()]
+    q = (torch.randn(1, nq, d, generator=g) * 2).to(dtype).double()
+    q[0, 5, 9] = 20.0; k[0][4000, 1, 9] = 20.0
+    kp, vp, table = make_paged(k, v, [n], page, dtype, seed=9)
+    assert table.shape[1] > 128
+    qrow = q.reshape(1, nq * d).to(dtype).to(DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    for window in (0, 3000):
+        out = torch.empty(1, nq * d, dtype=dtype, device=DEV)
+        ops.attention_decode(qrow, nq * d, kp.to(DEV), vp.to(DEV), table.to(DEV), slots, pos, out, nq, nkv, d, page, window,
+                             table.shape[1] * page, 1.0 / math.sqrt(d))
+        lo = max(0, n - window) if window else 0
+        want = plain.softmax_values(plain.attention_scores(q[0], k[0][lo:n], nq, nkv), v[0][lo:n], nq, nkv)
+        got = out[0].view(nq, d)
+        err = float((got.double().cpu() - want).abs().max())
+        assert err <= 2 ** -8 * float(want.abs().max()), f"window {window}: |diff| {err:.3e}"
+        if window == 0:
+            assert (got[5].double().cpu() - v[0][4000, 1]).abs().max() < 0.1
+
+
 @pytest.mark.parametrize("nq,nkv,d,window", [(4, 2, 16, 0), (6, 3, 48, 0), (3, 1, 80, 0), (8, 2, 128, 0), (2, 2, 256, 0),
                                              (4, 1, 64, 0), (5, 5, 112, 100), (4, 2, 32, 7), (2, 1, 96, 64)])
 def test_attention_prefill_flash(nq, nkv, d, window):
