@@ -440,6 +440,46 @@ def test_attention_prefill_flash(nq, nkv, d, window):
     assert not ops.lib().citlali_attention_prefill_supports(40, 64) and not ops.lib().citlali_attention_prefill_supports(128, 16)
 
 
+@pytest.mark.parametrize("nq,nkv,window", [(8, 2, 0), (3, 1, 0), (5, 5, 0), (4, 2, 100), (6, 2, 0), (3, 3, 150), (2, 1, 64)])
+def test_attention_prefill_tcgen05(nq, nkv, window):
+    """The tcgen05 prompt kernel alone (head size 128, pages of 64): groups with an even number of heads (two
+    heads a block) and with an odd one (two row tiles a block), runs of 48 to 700 new tokens with and without
+    cached tokens before them, several sequences in one launch, windows that end inside and across key tiles,
+    a far key that takes nearly all the weight, against the plain implementation."""
+    g = torch.Generator().manual_seed(nq * 7 + nkv + window)
+    dtype, d = torch.bfloat16, 128
+    assert ops.lib().citlali_attention_prefill_tc_supports(d, 64)
+    past, n_new = [0, 130, 5, 0, 63, 200, 1], [48, 257, 64, 129, 300, 700, 128]
+    k = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    v = [torch.randn(p + n, nkv, d, generator=g).to(dtype).double() for p, n in zip(past, n_new)]
+    qfull = [(torch.randn(p + n, nq, d, generator=g) * 1.5).to(dtype).double() for p, n in zip(past, n_new)]
+    qfull[5][850, :, 2] = 18.0; k[5][11, :, 2] = 18.0           # row 850 finds key 11 among 851
+    lengths = [p + n for p, n in zip(past, n_new)]
+    kp, vp, table = make_paged(k, v, lengths, 64, dtype, seed=6)
+    qq = torch.cat([qf[p:].reshape(-1, nq * d) for qf, p in zip(qfull, past)]).to(dtype)
+    pad = torch.randn(qq.shape[0], 8).to(dtype)
+    qrow = torch.cat([qq, pad], dim=1).contiguous().to(DEV)
+    out = torch.full((qq.shape[0], nq * d), 7.0, dtype=dtype, device=DEV)
+    starts = [0]
+    for n in n_new:
+        starts.append(starts[-1] + n)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    B = len(n_new)
+    ops.attention_prefill_tc(qrow, qrow.shape[1], kp.to(DEV), vp.to(DEV), table.to(DEV), i32(starts), i32(list(range(B))),
+                             i32(past), out, B, max(n_new), nq, nkv, d, 64, window, 1.0 / math.sqrt(d), error_flag=flag)
+    torch.cuda.synchronize()
+    assert flag.tolist() == [0, 0, 0, 0]
+    for b in range(B):
+        want = plain.causal_attention(qfull[b], k[b], v[b], nq, nkv, window=window or None)[past[b]:]
+        got = out[starts[b]:starts[b + 1]].view(-1, nq, d)
+        err = float((got.double().cpu() - want).abs().max())
+        # P is rounded to bfloat16 before it multiplies V: 2^-9 relative per term on top of the output's rounding
+        assert err <= 2 ** -7 * float(want.abs().max()), f"sequence {b}: |diff| {err:.3e} of {float(want.abs().max()):.3e}"
+    if window == 0:
+        assert (out[starts[5] + 650].view(nq, d)[0].double().cpu() - v[5][11, 0]).abs().max() < 0.1
+
+
 @pytest.mark.parametrize("M,inter,K", [(1, 192, 64), (8, 12288, 512), (70, 160, 96), (128, 48, 64), (129, 64, 128),
                                        (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024), (2048, 2048, 128),
                                        (1200, 1200, 64), (256, 1024, 2048), (300, 2048, 4096)])
