@@ -191,7 +191,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t it = 0, acc_it = 0;
+            // The tensor core takes few MMAs ahead of the one it runs, so what this thread does between the MMAs of
+            // one K block and those of the next is time the tensor core stands still: the stage and its phase
+            // are counted, not divided, and a stage's descriptors are the first stage's plus a constant (the
+            // address field counts 16-byte units; 32 bytes on for each 16-element K slice).
+            uint32_t acc_it = 0, stage = 0, phase = 0;
+            const uint64_t desc_a0 = smem_desc_sw128(smem_a, 0), desc_b0 = smem_desc_sw128(smem_b, 0);
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++acc_it) {
                 int ta, tb, sp;
@@ -201,16 +207,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(smem_u32(&acc_empty_bar[as]), ((acc_it / kAccStages) & 1u) ^ 1u, abort_flag, p.error_flag, 102)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + as * BN;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / kStages) & 1u, abort_flag, p.error_flag, 103)) { ok = false; break; }
+                uint32_t accumulate = 0;
+                // whether the stage of the K block about to be multiplied has landed is looked up before the MMAs of
+                // the block ahead of it are issued, so that between two blocks' MMAs there is only the commit
+                bool landed = kb0 < kb1 && mbar_try_wait(full0 + stage * 8u, phase);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!landed && !mbar_wait(full0 + stage * 8u, phase, abort_flag, p.error_flag, 103)) { ok = false; break; }
                     tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        mma_bf16(tmem_d, smem_desc_sw128(smem_a + s * kBytesA, k * 32), smem_desc_sw128(smem_b + s * kBytesB, k * 32),
-                                 kIdesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    }
-                    mma_commit(smem_u32(&empty_bar[s]));
+                    const uint64_t da = desc_a0 + (uint64_t)(stage * (kBytesA >> 4)), db = desc_b0 + (uint64_t)(stage * (kBytesB >> 4));
+                    const uint32_t this_empty = empty0 + stage * 8u;
+                    if (++stage == (uint32_t)kStages) { stage = 0; phase ^= 1u; }
+                    landed = kb + 1 < kb1 && mbar_try_wait(full0 + stage * 8u, phase);
+                    mma_bf16(tmem_d, da, db, kIdesc, accumulate);
+                    mma_bf16(tmem_d, da + 2, db + 2, kIdesc, 1u);
+                    mma_bf16(tmem_d, da + 4, db + 4, kIdesc, 1u);
+                    mma_bf16(tmem_d, da + 6, db + 6, kIdesc, 1u);
+                    mma_commit(this_empty);
+                    accumulate = 1u;
                 }
                 if (ok) mma_commit(smem_u32(&acc_full_bar[as]));
             }
