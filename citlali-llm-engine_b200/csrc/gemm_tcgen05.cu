@@ -67,6 +67,9 @@ constexpr int stages_for(bool swapped) {
     return swapped ? (BN <= 16 ? 5 : BN <= 64 ? 4 : BN <= 128 ? 3 : 4) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -295,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (m < p.M) {
                             const size_t o = (size_t)m * p.N + i;
                             if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[c]);
-                            else if (p.out_kind == kAddF32) outf[o] += v[c];
+                            else if (p.out_kind == kAddF32) red_add_f32(outf + o, v[c]);
                             else outf[o] = v[c];
                         }
                     }
@@ -461,7 +464,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else if (n < p.N && m < p.M) {
                         const size_t o = (size_t)m * p.N + n;
                         if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[e]);
-                        else if (p.out_kind == kAddF32) outf[o] += v[e];
+                        else if (p.out_kind == kAddF32) red_add_f32(outf + o, v[e]);      // one add per element: the same sum, no load to wait for
                         else outf[o] = v[e];
                     }
                 }
