@@ -30,7 +30,8 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
                           int nq, int nkv, int d, float eps, int write_cache, int heads_per_block) {
     extern __shared__ float2 cos_sin[];                 // [d / 2]: the row's rotation, shared by the block's heads
     dependents_may_launch();
-    wait_for_predecessor();
+    // positions, slots and page tables come from the host before the step: the rotation and the row's place in
+    // the cache are worked out while the kernel ahead (the projection) is still running
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int total = nq + 2 * nkv;
@@ -43,12 +44,13 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         cos_sin[i] = make_float2(cs, sn);
     }
-    __syncthreads();
     size_t page_off = 0;
     if (write_cache) {
         const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
         page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * d;       // + kv head * page_size * d
     }
+    __syncthreads();
+    wait_for_predecessor();
     T* row_ptr = qkv + (size_t)row * total * d;
 
     // a warp takes heads warp, warp + 8, ...; it loads kRopeBatch of them before it works on any
@@ -138,7 +140,7 @@ qk_norm_rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const TG* __restr
                               int nq, int nkv, int d, float eps, int write_cache, int heads_per_block, int lanes) {
     extern __shared__ float2 cos_sin[];                 // [d / 2]: the row's rotation, shared by the block's heads
     dependents_may_launch();
-    wait_for_predecessor();
+    // (as above: everything that does not come from the projection is done before waiting for it)
     const int row = blockIdx.x;
     const int total = nq + 2 * nkv;
     const int head_begin = blockIdx.y * heads_per_block;
@@ -150,12 +152,13 @@ qk_norm_rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const TG* __restr
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         cos_sin[i] = make_float2(cs, sn);
     }
-    __syncthreads();
     size_t page_off = 0;
     if (write_cache) {
         const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
         page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * d;       // + kv head * page_size * d
     }
+    __syncthreads();
+    wait_for_predecessor();
     __nv_bfloat16* row_ptr = qkv + (size_t)row * total * d;
     const int part = threadIdx.x % lanes, e0 = part * 8;      // this lane's elements e0..e0+7 of each half
     const int heads_per_pass = kRopeVecThreads / lanes;

@@ -66,10 +66,27 @@ rms_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
                      const int32_t* __restrict__ row_index, TO* __restrict__ out, int hidden, float eps) {
     __shared__ float scratch[32];
     dependents_may_launch();
-    wait_for_predecessor();
+    // the gains (weights) and the row's index (from the host) are fetched while the kernel ahead still runs
     const int row = blockIdx.x;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * hidden);
     const int quads = hidden >> 2;
+    float4 g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int q = threadIdx.x + j * 256;
+        g[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q < quads) {
+            if constexpr (sizeof(TG) == 2) {
+                const uint2 w = *reinterpret_cast<const uint2*>(gain + q * 4);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w.y));
+                g[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+                g[j] = *reinterpret_cast<const float4*>(gain + q * 4);
+            }
+        }
+    }
+    wait_for_predecessor();
     float4 v[8];
     float ss = 0.0f;
 #pragma unroll
@@ -87,8 +104,8 @@ rms_norm_rows_kernel(const float* __restrict__ x, const TG* __restrict__ gain,
         const int q = threadIdx.x + j * 256;
         if (q < quads) {
             const int i = q * 4;
-            const float a = v[j].x * inv * ldf(gain, i), b = v[j].y * inv * ldf(gain, i + 1);
-            const float c = v[j].z * inv * ldf(gain, i + 2), d = v[j].w * inv * ldf(gain, i + 3);
+            const float a = v[j].x * inv * g[j].x, b = v[j].y * inv * g[j].y;
+            const float c = v[j].z * inv * g[j].z, d = v[j].w * inv * g[j].w;
             if constexpr (sizeof(TO) == 2) {
                 __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
                 *reinterpret_cast<uint2*>(dst + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
@@ -138,7 +155,7 @@ extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
         return CITLALI_DISPATCH_FLOAT(out_dtype, TO, [&] {
-            if (hidden % 4 == 0 && hidden <= 8192)
+            if (hidden % 4 == 0 && hidden <= 8192 && (((uintptr_t)gain | (uintptr_t)x | (uintptr_t)out) & 15u) == 0)
                 launch_kernel(rms_norm_rows_kernel<TG, TO>, rows, 256, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
             else
                 launch_kernel(rms_norm_kernel<TG, TO>, rows, threads, 0, stream, x, (const TG*)gain, row_index, (TO*)out, hidden, eps);
