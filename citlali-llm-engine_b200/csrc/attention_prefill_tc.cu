@@ -145,6 +145,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
         abort_word = 0;
         mbar_init(smem_u32(&q_bar), 1);
         for (int i = 0; i < 2; ++i) {

@@ -68,6 +68,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
         abort_word = 0;
         for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&acc_full_bar[a]), 1); mbar_init(smem_u32(&acc_empty_bar[a]), 2 * kEpilogueWarps); }

@@ -68,6 +68,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 // One 2-D tile [box rows x box cols] from a row-major matrix into shared memory; completion
 // is counted in bytes on `bar`.  `c_inner` (elements along the row) must make a 16-byte
 // multiple; here it is always a multiple of 64 bfloat16.
