@@ -109,14 +109,17 @@ int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, in
 int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                     int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream);
 // The same product on pairs of SMs (tcgen05.mma with cta_group::2: a [256 x BN] tile per cluster of two
-// blocks, each fetching half of both operands).  Measured equal to the one-block kernel at 2,048 rows
-// (both run into the power limit), so it is off unless citlali_gemm_tc_set_pair_rows names a number of
-// rows of x from which citlali_gemm_tc uses it (0: never), on devices that run such clusters;
+// blocks, each fetching half of both operands).  With equal waves it takes 0.92-0.97 of the one-block
+// kernel's time at 512 to 4,096 rows and 0.82 at 8,192, and it loses where its 256-row tiles need a wave
+// more.  citlali_gemm_tc uses it from citlali_gemm_tc_set_pair_rows' number of rows on (512 unless set;
+// 0: never; the call returns the number that stood before) where the waves of pairs cost less, on devices
+// that run such clusters; citlali_gemm_tc_runs_on_pairs says whether a shape goes there, and
 // citlali_gemm_tc_pair_plan gives the tile width and the pairs that run at once.
 int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                          int mode, int32_t* error_flag, cudaStream_t stream);
 int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs);
 int citlali_gemm_tc_set_pair_rows(int rows);
+int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, int gate_runs);
 
 #ifdef __cplusplus
 }

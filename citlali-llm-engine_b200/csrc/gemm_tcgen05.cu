@@ -526,6 +526,7 @@ struct Plan {
     bool swapped;
     int bn;
     int splits;
+    long cost;      // normal form: waves x the tile's time in the model's units; 0 for the swapped form
 };
 
 // The plan is a function of the shape alone.
@@ -541,6 +542,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, b
     pl.swapped = false;
     pl.bn = 128;
     pl.splits = 1;
+    pl.cost = 0;
     long normal_tiles = (long)((M + kBM - 1) / kBM) * ((N + 127) / 128);
     if (N >= 192) {
         const int tiles_m = (M + kBM - 1) / kBM;
@@ -551,6 +553,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, b
             const long cost = ((tiles + sm_count - 1) / sm_count) * (2000 + 3 * bn);
             if (best < 0 || cost < best) { best = cost; pl.bn = bn; normal_tiles = tiles; }
         }
+        pl.cost = best;
     }
     if (M <= 128 || (M <= kMaxSwappedRows && normal_tiles < sm_count)) {
         pl.swapped = true;
@@ -599,11 +602,34 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams
 using namespace citlali;
 using namespace citlali::tc;
 
-static int g_pair_rows = 0;      // > 0: from this many rows of x on, the product runs on pairs of SMs
+// > 0: from this many rows of x on, the product runs on pairs of SMs where that fills the device's waves no
+// worse. Measured on Qwen3-8B's four projections at 256 to 8,192 rows: with equal waves the pair kernel takes
+// 0.92-0.97 of the one-block kernel's time (0.82 at 8,192 rows), and it loses where its 256-row tiles of one
+// width need a wave more; below 512 rows it never won.
+static int g_pair_rows = 512;
 
+// Sets the threshold and returns the one that stood before.
 extern "C" int citlali_gemm_tc_set_pair_rows(int rows) {
+    const int before = g_pair_rows;
     g_pair_rows = rows;
-    return 0;
+    return before;
+}
+
+// Whether the pair kernel takes this product: a normal-form plan, enough rows, and waves of pairs that cost
+// less than 0.95 of the one-block waves in the plan's own model.
+static bool runs_on_pairs(int M, int N, int K, const Plan& pl) {
+    if (pl.swapped || pl.cost <= 0 || g_pair_rows <= 0 || M < g_pair_rows) return false;
+    int bn = 0, pairs = 0;
+    citlali_gemm_tc_pair_plan(M, N, K, &bn, &pairs);
+    if (pairs <= 0) return false;
+    const long units = (long)((M + 2 * kBM - 1) / (2 * kBM)) * ((N + bn - 1) / bn);
+    const long pair_cost = ((units + pairs - 1) / pairs) * (2000 + 3 * bn);
+    return pair_cost * 95 < pl.cost * 100;
+}
+
+extern "C" int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, int gate_runs) {
+    if (sm_count <= 0) sm_count = 148;
+    return runs_on_pairs(M, N, K, make_plan(M, N, K, sm_count, 0, gate_runs != 0)) ? 1 : 0;
 }
 
 // How the product of this shape would run: *swapped, *bn and the K split (*splits).
@@ -649,11 +675,7 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
     }
     if (sm_count <= 0) sm_count = 148;
     const Plan pl = make_plan(M, N, K, sm_count, force_splits, swiglu);
-    if (!pl.swapped && g_pair_rows > 0 && M >= g_pair_rows) {
-        int bn = 0, pairs = 0;
-        citlali_gemm_tc_pair_plan(M, N, K, &bn, &pairs);
-        if (pairs > 0) return citlali_gemm_tc_pair(x, w, y, y_dtype, M, N, K, mode, error_flag, stream);
-    }
+    if (runs_on_pairs(M, N, K, pl)) return citlali_gemm_tc_pair(x, w, y, y_dtype, M, N, K, mode, error_flag, stream);
     GemmParams p;
     p.M = M; p.N = N; p.K = K;
     p.splits = pl.splits;

@@ -114,23 +114,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            uint32_t it = 0, acc_it = 0;
+            // as in the one-block kernel: stage and phase are counted, descriptors made by addition, and the next
+            // stage's barrier is looked up before the current MMAs are issued
+            uint32_t acc_it = 0, stage = 0, phase = 0;
+            const uint64_t desc_a0 = smem_desc_sw128(smem_a, 0), desc_b0 = smem_desc_sw128(smem_b, 0);
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             bool ok = true;
             for (int u = pair_id; u < units && ok; u += pairs, ++acc_it) {
                 const int as = acc_it % kAccStages;
                 if (!mbar_wait(smem_u32(&acc_empty_bar[as]), ((acc_it / kAccStages) & 1u) ^ 1u, abort_flag, p.error_flag, 302)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + as * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (it / kStages) & 1u, abort_flag, p.error_flag, 303)) { ok = false; break; }
+                uint32_t accumulate = 0;
+                bool landed = kblocks > 0 && mbar_try_wait(full0 + stage * 8u, phase);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!landed && !mbar_wait(full0 + stage * 8u, phase, abort_flag, p.error_flag, 303)) { ok = false; break; }
                     tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        mma_bf16_pair(tmem_d, smem_desc_sw128(smem_a + s * kBytesA, k * 32), smem_desc_sw128(smem_b + s * kBytesB, k * 32),
-                                      kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    }
-                    mma_commit_pair(smem_u32(&empty_bar[s]), 3);
+                    const uint64_t da = desc_a0 + (uint64_t)(stage * (kBytesA >> 4)), db = desc_b0 + (uint64_t)(stage * (kBytesB >> 4));
+                    const uint32_t this_empty = empty0 + stage * 8u;
+                    if (++stage == (uint32_t)kStages) { stage = 0; phase ^= 1u; }
+                    landed = kb + 1 < kblocks && mbar_try_wait(full0 + stage * 8u, phase);
+                    mma_bf16_pair(tmem_d, da, db, kIdesc, accumulate);
+                    mma_bf16_pair(tmem_d, da + 2, db + 2, kIdesc, 1u);
+                    mma_bf16_pair(tmem_d, da + 4, db + 4, kIdesc, 1u);
+                    mma_bf16_pair(tmem_d, da + 6, db + 6, kIdesc, 1u);
+                    mma_commit_pair(this_empty, 3);
+                    accumulate = 1u;
                 }
                 if (ok) mma_commit_pair(smem_u32(&acc_full_bar[as]), 3);
             }

@@ -272,9 +272,15 @@ def gemm_tc_pair_plan(M: int, N: int, K: int) -> dict:
     return {"bn": bn.value, "pairs": pairs.value}
 
 
-def gemm_tc_set_pair_rows(rows: int) -> None:
-    """From ``rows`` rows of ``x`` on, ``gemm_tc`` runs on pairs of SMs (0: never)."""
-    lib().citlali_gemm_tc_set_pair_rows(_i(rows))
+def gemm_tc_set_pair_rows(rows: int) -> int:
+    """From ``rows`` rows of ``x`` on, ``gemm_tc`` runs on pairs of SMs where their waves cost less
+    (0: never). Returns the number that stood before."""
+    return int(lib().citlali_gemm_tc_set_pair_rows(_i(rows)))
+
+
+def gemm_tc_runs_on_pairs(M: int, N: int, K: int, device, swiglu: bool = False) -> bool:
+    """Whether ``gemm_tc`` gives a product of this shape to the pair kernel."""
+    return bool(lib().citlali_gemm_tc_runs_on_pairs(_i(M), _i(N), _i(K), _i(sm_count(device)), _i(1 if swiglu else 0)))
 
 
 def gemm_tc_pair(x, w, y, accumulate=False, error_flag=None, swiglu=False):

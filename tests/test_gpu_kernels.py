@@ -289,11 +289,23 @@ def test_sample_rows_follows_the_cdf(V):
         assert math.isfinite(float(logits[r, tok[r]]))
 
 
+@pytest.fixture(params=["as planned", "one block"])
+def one_block_or_pairs(request):
+    """Runs a test of gemm_tc twice: with the dispatch as it stands, and with the pair kernel off, so that
+    the one-block kernel is tested at many rows too."""
+    if request.param == "one block":
+        before = ops.gemm_tc_set_pair_rows(0)
+        yield
+        ops.gemm_tc_set_pair_rows(before)
+    else:
+        yield
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (5, 192, 64), (17, 1000, 96), (33, 130, 200), (64, 4096, 512),
                                    (100, 24, 4096), (128, 256, 512), (129, 256, 128), (300, 520, 200),
                                    (1000, 96, 72), (2048, 512, 1024), (1, 4096, 12288), (256, 4096, 4096), (200, 1000, 12288),
                                    (512, 4096, 2048)])
-def test_gemm_tc(M, N, K):
+def test_gemm_tc(M, N, K, one_block_or_pairs):
     """The tensor-core product in both of its forms (weights on the wide side for few rows, rows
     on the wide side for many), with sizes that are no multiple of any tile, K that is split and
     K that is not, every output kind."""
@@ -483,7 +495,7 @@ def test_attention_prefill_tcgen05(nq, nkv, window):
 @pytest.mark.parametrize("M,inter,K", [(1, 192, 64), (8, 12288, 512), (70, 160, 96), (128, 48, 64), (129, 64, 128),
                                        (400, 208, 120), (8, 2048, 4096), (33, 1024, 1024), (2048, 2048, 128),
                                        (1200, 1200, 64), (256, 1024, 2048), (300, 2048, 4096)])
-def test_gemm_tc_gate_epilogue(M, inter, K):
+def test_gemm_tc_gate_epilogue(M, inter, K, one_block_or_pairs):
     """silu(gate) * up straight from the product's epilogue, in both forms and with K split."""
     g = torch.Generator().manual_seed(M + inter)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -529,18 +541,30 @@ def test_gemm_tc_on_pairs_of_sms(M, N, K):
         act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
         ops.gemm_tc_pair(xd, packed.to(DEV), act, swiglu=True, error_flag=flag)
         close(act, plain.swiglu(x.double() @ wg.double().t(), x.double() @ wu.double().t()), torch.bfloat16)
-    # the one-block kernel and the pair kernel add the K blocks in the same order
-    one = torch.empty(M, N, device=DEV)
-    ops.gemm_tc(xd, wd, one, error_flag=flag)
+    # the one-block kernel and the pair kernel add the K blocks in the same order; gemm_tc's own dispatch
+    # gives the product to the one that its plan names
+    one, two = torch.empty(M, N, device=DEV), torch.empty(M, N, device=DEV)
+    before = ops.gemm_tc_set_pair_rows(0)
     try:
+        assert not ops.gemm_tc_runs_on_pairs(M, N, K, DEV)
+        ops.gemm_tc(xd, wd, one, error_flag=flag)
         ops.gemm_tc_set_pair_rows(128)
-        two = torch.empty(M, N, device=DEV)
         ops.gemm_tc(xd, wd, two, error_flag=flag)
+        assert torch.equal(two, y32 if ops.gemm_tc_runs_on_pairs(M, N, K, DEV) else one)
     finally:
-        ops.gemm_tc_set_pair_rows(0)
-    assert torch.equal(two, y32)
-    assert float((one - two).abs().max()) <= 2e-6 * scale
+        ops.gemm_tc_set_pair_rows(before)
+    assert float((one - y32).abs().max()) <= 2e-6 * scale
     assert flag.tolist() == [0, 0, 0, 0]
+
+
+def test_gemm_tc_pairs_where_their_waves_cost_less():
+    """Prompts of Qwen3-8B's widths: the shapes that were measured faster on pairs go there, the others do not."""
+    if ops.gemm_tc_pair_plan(2048, 4096, 4096)["pairs"] != 74 or ops.sm_count(DEV) != 148:
+        pytest.skip("the expectations are those of 148 SMs")
+    for (M, N, K, gate, want) in [(2048, 6144, 4096, False, True), (2048, 4096, 12288, False, True), (2048, 24576, 4096, True, True),
+                                  (1536, 4096, 12288, False, False), (1024, 6144, 4096, False, False), (512, 24576, 4096, True, True),
+                                  (384, 24576, 4096, True, False), (768, 4096, 4096, False, False), (8192, 4096, 4096, False, True)]:
+        assert ops.gemm_tc_runs_on_pairs(M, N, K, DEV, swiglu=gate) == want, (M, N, K)
 
 
 def test_gemm_tc_split_k_sums_in_one_order():
