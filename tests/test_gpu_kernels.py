@@ -510,7 +510,7 @@ def test_gemm_tc_gate_epilogue(M, inter, K, one_block_or_pairs):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (130, 144, 72), (1000, 1000, 512), (2048, 4096, 1024),
-                                   (513, 96, 4096)])
+                                   (513, 96, 4096), (700, 1300, 2048), (2048, 4096, 4096)])
 def test_gemm_tc_on_pairs_of_sms(M, N, K):
     """The product with cta_group::2 (two blocks of a cluster on one [256 x BN] tile), every output kind,
     sizes that are no multiple of any tile; and the same through gemm_tc's own dispatch."""
@@ -526,6 +526,9 @@ def test_gemm_tc_on_pairs_of_sms(M, N, K):
     ops.gemm_tc_pair(xd, wd, y32, error_flag=flag)
     err = float((y32.double().cpu() - want).abs().max())
     assert err <= 1e-5 * scale * max(1.0, math.sqrt(K / 64)), f"float32 out: |diff| {err:.3e} of {scale:.3e}"
+    again = torch.full((M, N), -3.0, device=DEV)
+    ops.gemm_tc_pair(xd, wd, again, error_flag=flag)
+    assert torch.equal(again, y32)
     y16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     ops.gemm_tc_pair(xd, wd, y16, error_flag=flag)
     close(y16, want, torch.bfloat16)
