@@ -1,6 +1,6 @@
 """The benchmark's layer sizes (hidden 4096, 32 / 8 heads of 128, feed-forward 12288, vocabulary 151936) with two
 layers and random weights: the bfloat16 engine, whose kernels take their production shapes here (both forms of the
-tensor-core product with K splits over clusters, the tcgen05 prompt attention, the cluster decode attention, the wide
+tensor-core product with K splits over clusters, the product on pairs of SMs, the tcgen05 prompt attention, the cluster decode attention, the wide
 argmax), against the 32-bit engine on the same weight values; and the 32-bit engine against itself under another
 way of cutting the tokens.  No plain-implementation run at this size: the 32-bit engine is checked against it on
 the tiny configurations."""
@@ -8,6 +8,7 @@ import pytest
 import torch
 
 import citlali_b200 as cb
+from citlali_b200 import ops
 from helpers import random_tokens
 
 pytestmark = pytest.mark.gpu
@@ -59,14 +60,18 @@ def run(session, requests, cuts, want_tail):
 def test_production_shapes_agree_with_the_32_bit_path(sessions):
     s32, s16 = sessions
     vocab = SHAPE["vocab_size"]
-    requests = [("a", random_tokens(vocab, 300, 1)), ("b", random_tokens(vocab, 17, 2)), ("c", random_tokens(vocab, 130, 3))]
-    whole32 = run(s32, requests, [300, 17, 130], 8)
-    cut32 = run(s32, requests, [268, 1, 129], 8)             # other cuts: the last tokens one by one
-    assert set(whole32) == set(cut32) and len(whole32) == 24
+    requests = [("a", random_tokens(vocab, 300, 1)), ("b", random_tokens(vocab, 17, 2)), ("c", random_tokens(vocab, 130, 3)),
+                ("d", random_tokens(vocab, 200, 4))]
+    # 647 rows in the first step: the gate/up product of that many rows runs on pairs of SMs where the device has them
+    if ops.gemm_tc_pair_plan(647, 2 * SHAPE["intermediate_size"], SHAPE["hidden_size"])["pairs"] >= 74:
+        assert ops.gemm_tc_runs_on_pairs(647, 2 * SHAPE["intermediate_size"], SHAPE["hidden_size"], "cuda:0", swiglu=True)
+    whole32 = run(s32, requests, [300, 17, 130, 200], 8)
+    cut32 = run(s32, requests, [268, 1, 129, 180], 8)             # other cuts: the last tokens one by one
+    assert set(whole32) == set(cut32) and len(whole32) == 32
     for key in whole32:
         assert torch.equal(whole32[key], cut32[key]), f"32-bit logits depend on the cut at {key}"
-    whole16 = run(s16, requests, [300, 17, 130], 8)
-    cut16 = run(s16, requests, [268, 1, 129], 8)
+    whole16 = run(s16, requests, [300, 17, 130, 200], 8)
+    cut16 = run(s16, requests, [268, 1, 129, 180], 8)
     worst = 0.0
     for key, ref in whole32.items():
         scale = float(ref.abs().max())
