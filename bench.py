@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload 3|4 [--repetitions R]      the batch workloads of BASELINE.json's other shapes
 
 Prints ONE JSON line.  ``value`` is decoded tokens a second at batch 8 with every sequence
 near the context length of the benchmark configuration (device time, CUDA events around K
@@ -66,6 +67,91 @@ def peaks():
     return dict(FALLBACK_PEAKS, source="fallback")
 
 
+def workload_from_baseline(index):
+    """A batch workload of BASELINE.json's configs (a sentence): the model's sizes, the number of
+    prompts, the range of their lengths and the decode steps."""
+    with open(os.path.join(ROOT, "BASELINE.json")) as f:
+        text = json.load(f)["configs"][index]
+    def num(pattern):
+        m = re.search(pattern, text)
+        if not m:
+            raise SystemExit(f"bench.py: configs[{index}] of BASELINE.json does not say '{pattern}'")
+        return int(m.group(1).replace(",", ""))
+    span = re.search(r"lengths uniform in \[(\d+),\s*(\d+)\]", text)
+    if not span:
+        raise SystemExit(f"bench.py: configs[{index}] of BASELINE.json names no range of prompt lengths")
+    return dict(name=text.split(":")[0].strip(), num_hidden_layers=num(r"(\d+) layers"), hidden_size=num(r"hidden (\d+)"),
+                num_attention_heads=num(r"(\d+) q heads"), num_key_value_heads=num(r"(\d+) kv heads"),
+                head_dim=num(r"head_dim (\d+)"), intermediate_size=num(r"intermediate (\d+)"),
+                vocab_size=num(r"vocab (\d+)"), tie_word_embeddings="untied" not in text,
+                prompts=num(r"Batch of (\d+) prompts"), shortest=int(span.group(1)), longest=int(span.group(2)),
+                decode_steps=num(r"then (\d+) decode steps"))
+
+
+def run_workload(index, repetitions):
+    """One of BASELINE.json's batch workloads through ``InferenceSession.generate``: unequal prompts in
+    one step, then the decode steps, host tokens in and out.  Prints one JSON line: decoded tokens a
+    second (the median run), the prompts' tokens a second, and both against their rooflines."""
+    import torch
+    import citlali_b200 as cb
+
+    w = workload_from_baseline(index)
+    context = -(-(w["longest"] + w["decode_steps"]) // 64) * 64
+    cfg = cb.config_from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], num_hidden_layers=w["num_hidden_layers"], hidden_size=w["hidden_size"],
+        num_attention_heads=w["num_attention_heads"], num_key_value_heads=w["num_key_value_heads"], head_dim=w["head_dim"],
+        intermediate_size=w["intermediate_size"], vocab_size=w["vocab_size"], rope_theta=1e6, rms_norm_eps=1e-6,
+        tie_word_embeddings=w["tie_word_embeddings"], max_position_embeddings=max(context, 40960)))
+    pk = peaks()
+    session = cb.InferenceSession().load_random(cfg, seed=1, max_context=context, dtype="bfloat16", device="cuda:0",
+                                                max_batch=w["prompts"])
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(w["shortest"], w["longest"]))]
+               for _ in range(w["prompts"])]
+    options = cb.GenerationOptions(max_new_tokens=w["decode_steps"], max_context=context, stop_ids=[])
+    clocks = ClockSampler()
+    runs = []
+    for rep in range(1 + repetitions):
+        if rep == 1:
+            clocks.start()
+        torch.cuda.synchronize()
+        session.generate(prompts, options)
+        torch.cuda.synchronize()
+        if rep >= 1:
+            runs.append(dict(session.stats))
+        print(f"[bench] {w['name']} run {rep}: {session.stats}", file=sys.stderr, flush=True)
+    clock_record = clocks.stop()
+    run = sorted(runs, key=lambda r: r["decode_s"])[len(runs) // 2]
+    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv, layers = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.num_hidden_layers
+    layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I
+    tokens = sum(len(p) for p in prompts)
+    prefill_flops = (2.0 * tokens * layer_params * layers + 2.0 * H * cfg.vocab_size * len(prompts)
+                     + layers * 4.0 * sum(n * (n + 1) / 2 for n in map(len, prompts)) * d * nq)
+    kv_bytes_per_token = sum(2 * g.requirement.num_kv_heads * g.requirement.head_dim * 2 * len(g.steps)
+                             for g in session.cache.kv_groups)
+    steps = run["decode_tokens"] / len(prompts)
+    step_bytes = session.model.weight_bytes_read_per_step() + (tokens + len(prompts) * steps / 2) * kv_bytes_per_token
+    decode_ms = run["decode_s"] / steps * 1e3
+    achieved = step_bytes / (decode_ms / 1e3) / 1e9
+    print(json.dumps({
+        "metric": f"decode tok/s, {len(prompts)} unequal prompts ({w['name']}, random bf16 weights)",
+        "value": run["decode_tokens"] / run["decode_s"], "unit": "tok/s", "n_gpus": 1, "steps": int(steps), "warmup": 1,
+        "ms_per_step": decode_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
+        "timing": "host clock around InferenceSession.generate's prompt step and decode steps, tokens from and to the host",
+        "config": {"model": w["name"], "layers": layers, "hidden": H, "q_heads": nq, "kv_heads": nkv, "head_dim": d,
+                   "intermediate": I, "vocab": cfg.vocab_size, "global_batch": len(prompts), "prompt_tokens": tokens,
+                   "shortest": min(map(len, prompts)), "longest": max(map(len, prompts)), "decode_steps": int(steps),
+                   "repetitions": repetitions, "parallelism": "single GPU", "peaks": pk["source"]},
+        "prefill": {"value": tokens / run["prefill_s"], "tokens": tokens, "ms": run["prefill_s"] * 1e3,
+                    "frac": prefill_flops / run["prefill_s"] / (pk["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+        "clocks": clock_record}))
+    return 0
+
+
 class ClockSampler:
     """nvidia-smi in the background while something is timed."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -124,6 +210,9 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", type=int, default=2,
+                    help="which of BASELINE.json's configs to run: 2 (the benchmark configuration) or a batch workload (3, 4)")
+    ap.add_argument("--repetitions", type=int, default=5, help="timed runs of a batch workload (the median is reported)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -134,6 +223,9 @@ def main():
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2
+
+    if args.workload != 2:
+        return run_workload(args.workload, max(1, args.repetitions))
 
     import torch
     import citlali_b200 as cb
