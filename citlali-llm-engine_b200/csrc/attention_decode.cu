@@ -202,40 +202,34 @@ attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunk
     }
 }
 
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// One float at shared-memory address `addr` of the block with rank `rank` in this cluster.
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// One float to shared-memory address `addr` of the block with rank `rank` in this cluster.
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, float v) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 // The same work on the tensor cores, for pages of 64 keys.  The rows of the MMA are the query
 // heads that share the key/value head (padded to 16), so a key or value read from the cache
 // serves all of them.  The block walks its chunk one page at a time (cp.async, double-buffered);
 // each warp takes 16 keys of the page: S = Q K^T (mma.sync m16n8k16), online softmax in float,
-// O += P V.  At the end the four warps' (m, l, O) are merged through shared memory and written
-// as the chunk's partial, maxima in log2 units.
+// O += P V.  At the end the four warps' (m, l, O) are folded through shared memory (maxima in log2
+// units), and the blocks of a cluster send their runs of a head to the block that merges that head.
 constexpr int kMaxClusterBlocks = 16;     // blocks per (sequence, head group): a cluster, at most the non-portable size
 
-// Block `rank` of a cluster merges heads rank, rank + split, ... over the (m, l, O) that every block of
-// the cluster holds at `part_addr`, in rank order.  All blocks' (m, l) are read at once, then all their
-// values of an output element at once: the loads of a round are independent, so a round costs one trip
-// through the cluster, not one per block.
+// Block `rank` of a cluster merges heads rank, rank + split, ... over the (m, l, O) of all blocks' runs, which
+// they have sent to `gathered` ([head / split][sender][D + 2]), in rank order.
 template <int kBlocks, int D>
-__device__ __forceinline__ void merge_cluster_heads(uint32_t part_addr, __nv_bfloat16* out_row, int rank, int split, int heads_here, int tid) {
+__device__ __forceinline__ void merge_gathered_heads(const float* gathered, __nv_bfloat16* out_row, int rank, int split, int heads_here, int tid) {
     for (int h = rank; h < heads_here; h += split) {
-        const uint32_t head_addr = part_addr + (uint32_t)(h * (D + 2)) * 4u;
+        const float* base = gathered + (size_t)((h / split) * split) * (D + 2);
         float mz[kBlocks], wz[kBlocks];
 #pragma unroll
         for (int z = 0; z < kBlocks; ++z) {
-            mz[z] = z < split ? ld_cluster_f32(head_addr, z) : -INFINITY;
-            wz[z] = z < split ? ld_cluster_f32(head_addr + 4u, z) : 0.0f;           // l for now
+            mz[z] = z < split ? base[(size_t)z * (D + 2)] : -INFINITY;
+            wz[z] = z < split ? base[(size_t)z * (D + 2) + 1] : 0.0f;           // l for now
         }
         float M = -INFINITY;
 #pragma unroll
@@ -249,14 +243,10 @@ __device__ __forceinline__ void merge_cluster_heads(uint32_t part_addr, __nv_bfl
         }
         const float inv = 1.0f / L;
         for (int i = tid; i < D; i += 128) {
-            float v[kBlocks];
-#pragma unroll
-            for (int z = 0; z < kBlocks; ++z)
-                v[z] = (z < split && mz[z] != -INFINITY) ? ld_cluster_f32(head_addr + (uint32_t)(2 + i) * 4u, z) : 0.0f;
             float a = 0.0f;
 #pragma unroll
             for (int z = 0; z < kBlocks; ++z)
-                if (z < split && mz[z] != -INFINITY) a = fmaf(v[z], wz[z], a);
+                if (z < split && mz[z] != -INFINITY) a = fmaf(base[(size_t)z * (D + 2) + 2 + i], wz[z], a);
             out_row[(size_t)h * D + i] = __float2bfloat16_rn(a * inv);
         }
     }
@@ -397,74 +387,75 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         __syncthreads();
     }
     cp_async_wait<0>();
+    // This block no longer reads its tile buffers: it says so to the cluster at once and waits for the others
+    // only before it writes into theirs.
+    if (split > 1) cluster_arrive();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-    // park every warp's (m in log2 units, l, O) over the tile buffers, then merge per head
+    // park every warp's (m in log2 units, l, O) of the rows that hold heads over the tile buffers
     float* park = reinterpret_cast<float*>(smem + 16 * kRowBytes);                // [4 warps][16 rows][D + 2]
     {
         const int r0 = lane >> 2, r1 = r0 + 8, col = (lane & 3) * 2;
         float* w0 = park + ((size_t)warp * 16 + r0) * (D + 2);
         float* w1 = park + ((size_t)warp * 16 + r1) * (D + 2);
-        if ((lane & 3) == 0) {
-            w0[0] = m0 == -INFINITY ? -INFINITY : m0 * scale_log2; w0[1] = l0;
-            w1[0] = m1 == -INFINITY ? -INFINITY : m1 * scale_log2; w1[1] = l1;
-        }
+        if (r0 < heads_here) {
+            if ((lane & 3) == 0) { w0[0] = m0 == -INFINITY ? -INFINITY : m0 * scale_log2; w0[1] = l0; }
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            w0[2 + i * 8 + col] = o[i][0]; w0[2 + i * 8 + col + 1] = o[i][1];
-            w1[2 + i * 8 + col] = o[i][2]; w1[2 + i * 8 + col + 1] = o[i][3];
+            for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(w0 + 2 + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+        }
+        if (r1 < heads_here) {
+            if ((lane & 3) == 0) { w1[0] = m1 == -INFINITY ? -INFINITY : m1 * scale_log2; w1[1] = l1; }
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(w1 + 2 + i * 8 + col) = make_float2(o[i][2], o[i][3]);
         }
     }
     __syncthreads();
-    // the four warps' results folded into one (m, l, O) per head: first into registers, then over `park`
-    constexpr int kPerThread = (16 * (D + 2) + 127) / 128;
-    float folded[kPerThread];
+    // element e = (head, i) of the four warps' results folded into one (m, l, O) per head
+    auto folded = [&](int e) {
+        const int h = e / (D + 2), i = e % (D + 2);
+        float M = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < kPerThread; ++k) {
-        const int e = tid + 128 * k;
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, park[((size_t)w * 16 + h) * (D + 2)]);
+        if (i == 0) return M;
         float v = 0.0f;
-        if (e < heads_here * (D + 2)) {
-            const int h = e / (D + 2), i = e % (D + 2);
-            float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) M = fmaxf(M, park[((size_t)w * 16 + h) * (D + 2)]);
-            if (i == 0) {
-                v = M;
-            } else {
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const float mw = park[((size_t)w * 16 + h) * (D + 2)];
-                    const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
-                    v = fmaf(park[((size_t)w * 16 + h) * (D + 2) + i], f, v);
-                }
-            }
+        for (int w = 0; w < 4; ++w) {
+            const float mw = park[((size_t)w * 16 + h) * (D + 2)];
+            const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
+            v = fmaf(park[((size_t)w * 16 + h) * (D + 2) + i], f, v);
         }
-        folded[k] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < kPerThread; ++k) {
-        const int e = tid + 128 * k;
-        if (e < heads_here * (D + 2)) park[e] = folded[k];          // [head][D + 2]
-    }
-    // Every block of the cluster now holds its run's (m, l, O) for each head.  After a cluster barrier
-    // block `rank` merges heads rank, rank + split, ... over all blocks, in rank order, reading the
-    // others' shared memory, and writes the output; a second barrier keeps that memory alive meanwhile.
-    __syncthreads();
-    if (split > 1) cluster_barrier();
-    const uint32_t part_addr = s_q + 16 * kRowBytes;
+        return v;
+    };
+    const int elems = heads_here * (D + 2);
+    float* gathered = park + 4 * 16 * (D + 2);       // behind the parked rows: what this block merges
     __nv_bfloat16* out_row = out + (size_t)row * out_stride + (size_t)head0 * D;
     if (split == 1) {
+        for (int e = tid; e < elems; e += 128) gathered[e] = folded(e);
+        __syncthreads();
         for (int e = tid; e < heads_here * D; e += 128) {
             const int h = e / D, i = e % D;
-            out_row[(size_t)h * D + i] = __float2bfloat16_rn(park[h * (D + 2) + 2 + i] * (1.0f / park[h * (D + 2) + 1]));
+            out_row[(size_t)h * D + i] = __float2bfloat16_rn(gathered[h * (D + 2) + 2 + i] * (1.0f / gathered[h * (D + 2) + 1]));
         }
-    } else if (split <= 2) merge_cluster_heads<2, D>(part_addr, out_row, rank, split, heads_here, tid);
-    else if (split <= 4) merge_cluster_heads<4, D>(part_addr, out_row, rank, split, heads_here, tid);
-    else if (split <= 8) merge_cluster_heads<8, D>(part_addr, out_row, rank, split, heads_here, tid);
-    else merge_cluster_heads<kMaxClusterBlocks, D>(part_addr, out_row, rank, split, heads_here, tid);
-    if (split > 1) cluster_barrier();
+        return;
+    }
+    // Head h is merged by block h % split.  Every block sends its (m, l, O) of a head into that block's shared
+    // memory, to [h / split][sender]: once all blocks are past their tiles (the barrier they arrived at
+    // above), the space behind a block's parked rows is free.  After one more barrier a block finds all
+    // runs of its heads in its own memory, merges them in rank order and leaves; nobody reads its memory after
+    // that barrier, so none is needed at the end.
+    cluster_wait();
+    const uint32_t gathered_addr = s_q + 16 * kRowBytes + 4 * 16 * (D + 2) * 4;
+    for (int e = tid; e < elems; e += 128) {
+        const int h = e / (D + 2), i = e % (D + 2);
+        st_cluster_f32(gathered_addr + (uint32_t)((((h / split) * split + rank) * (D + 2)) + i) * 4u, (uint32_t)(h % split), folded(e));
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (split <= 2) merge_gathered_heads<2, D>(gathered, out_row, rank, split, heads_here, tid);
+    else if (split <= 4) merge_gathered_heads<4, D>(gathered, out_row, rank, split, heads_here, tid);
+    else if (split <= 8) merge_gathered_heads<8, D>(gathered, out_row, rank, split, heads_here, tid);
+    else merge_gathered_heads<kMaxClusterBlocks, D>(gathered, out_row, rank, split, heads_here, tid);
 }
 
 static int g_forced_split = 0;     // > 0: blocks per (sequence, head group), for tuning
@@ -474,7 +465,8 @@ static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, con
                      int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
                      int rows, int nq, int nkv, int window, float scale, int split, cudaStream_t stream) {
     constexpr int tiles = (16 + 2 * kStagesKV * 64) * (D * 2 + 16);
-    constexpr int park = 16 * (D * 2 + 16) + 4 * 16 * (D + 2) * 4;
+    // the query rows, the four warps' parked rows, and behind them what the cluster's blocks send (at most 31 runs)
+    constexpr int park = 16 * (D * 2 + 16) + (4 * 16 + 32) * (D + 2) * 4;
     constexpr int smem = tiles > park ? tiles : park;
     auto kernel = attention_decode_tc_kernel<D, kStagesKV>;
     static bool configured = false;
