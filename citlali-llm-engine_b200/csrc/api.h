@@ -119,6 +119,10 @@ int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y_dtype, int
                          int mode, int32_t* error_flag, cudaStream_t stream);
 int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs);
 int citlali_gemm_tc_set_pair_rows(int rows);
+// The kernels' bounded wait on its own: a block waits `limit_ns` (at most one second) on a barrier on which
+// nothing arrives, gives up, records code 900 in error_flag[1] and its block in error_flag[2], and leaves
+// normally; result[0] = the wait's return value (0), result[1] = the block's abort word (1).
+int citlali_wait_selftest(int32_t* error_flag, int* result, long long limit_ns, cudaStream_t stream);
 int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, int gate_runs);
 
 #ifdef __cplusplus

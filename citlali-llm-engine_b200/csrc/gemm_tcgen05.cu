@@ -632,6 +632,36 @@ extern "C" int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, 
     return runs_on_pairs(M, N, K, make_plan(M, N, K, sm_count, 0, gate_runs != 0)) ? 1 : 0;
 }
 
+// The bounded wait of the tensor-core kernels, on its own: one block waits on an mbarrier on which nothing ever
+// arrives, with `limit_ns` instead of the kernels' two seconds.  The wait gives up, records code 900 and the
+// block in error_flag[1..2] and raises the block's abort word, which the other threads see; the kernel then
+// leaves normally.  result[0] = what the wait returned (0), result[1] = the abort word as thread 32 saw it.
+__global__ void wait_selftest_kernel(int32_t* error_flag, unsigned long long limit_ns, int* result) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(smem_u32(&bar), 0, abort_flag, error_flag, 900, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0) result[0] = ok ? 1 : 0;
+    if (threadIdx.x == 32) result[1] = *abort_flag;
+}
+
+extern "C" int citlali_wait_selftest(int32_t* error_flag, int* result, long long limit_ns, cudaStream_t stream) {
+    if (limit_ns < 0 || limit_ns > 1000000000ll) {
+        set_last_error("wait_selftest: the limit must lie between 0 and one second");
+        return kBadShape;
+    }
+    wait_selftest_kernel<<<1, 64, 0, stream>>>(error_flag, (unsigned long long)limit_ns, result);
+    return CITLALI_LAUNCH_CHECK();
+}
+
 // How the product of this shape would run: *swapped, *bn and the K split (*splits).
 extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits) {
     if (sm_count <= 0) sm_count = 148;

@@ -48,14 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // block has given up (`*abort_flag`), or after kWaitLimitNs, in which case it records `code`
 // in error_flag[1] (and the block in error_flag[2]) and raises the block's abort flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* error_flag, int code) {
+                                          int32_t* error_flag, int code, uint64_t limit_ns = kWaitLimitNs) {
     uint64_t start = 0;
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 31u) == 0u) {
             if (*abort_flag) return false;
             if (start == 0) start = global_timer();         // the clock is read only once the wait is long
-            if (global_timer() - start > kWaitLimitNs) {
+            if (global_timer() - start > limit_ns) {
                 *abort_flag = 1;
                 if (error_flag) {
                     atomicExch(error_flag + 1, code);

@@ -265,6 +265,18 @@ def gemm_tc_plan(M: int, N: int, K: int, device, force_splits: int = 0) -> dict:
     return {"swapped": bool(swapped.value), "bn": bn.value, "splits": splits.value}
 
 
+def wait_selftest(error_flag: torch.Tensor, limit_ms: float = 2.0):
+    """Run the tensor-core kernels' bounded wait on a barrier nothing arrives on; it gives up after
+    ``limit_ms``.  Returns (the wait's return value, the block's abort word); ``error_flag[1..2]`` hold
+    code 900 and the block."""
+    _need_cuda(error_flag)
+    result = torch.full((2,), -1, dtype=torch.int32, device=error_flag.device)
+    _check(lib().citlali_wait_selftest(_ptr(error_flag), _ptr(result), ctypes.c_longlong(int(limit_ms * 1e6)), _stream()),
+           "wait_selftest")
+    ok, abort = result.tolist()
+    return ok, abort
+
+
 def gemm_tc_pair_plan(M: int, N: int, K: int) -> dict:
     """The pair kernel's tile width for this shape and how many clusters of two the device runs at once."""
     bn, pairs = ctypes.c_int(), ctypes.c_int()

@@ -84,6 +84,35 @@ def test_embed_rows_and_the_fault_word(dtype):
     assert flag[0].item() == 1 and float(out[1].abs().sum()) == 0.0 and float(out[0].abs().sum()) > 0
 
 
+def test_a_wait_that_runs_out_reports_and_leaves_the_device_usable():
+    """The tensor-core kernels wait on their barriers through one function that gives up after a time limit.
+    Here it waits two milliseconds on a barrier on which nothing arrives: it returns false, raises the block's
+    abort word for the other threads, records its code and block in the fault word, and the kernel ends
+    normally; a session that owns the fault word reports it and clears it, and the next product is right."""
+    import tempfile
+    from helpers import make_model_dir
+    with tempfile.TemporaryDirectory() as tmp:
+        make_model_dir(tmp, "A", "bfloat16")
+        session = cb.InferenceSession().load_model(tmp, max_context=64, dtype="bfloat16", max_batch=2)
+        flag = session.model.ctx.error_flag
+        assert flag.tolist() == [0, 0, 0, 0]
+        ok, abort = ops.wait_selftest(flag, limit_ms=2.0)
+        assert (ok, abort) == (0, 1)
+        assert flag.tolist()[1:3] == [900, 0]
+        with pytest.raises(cb.CitlaliError, match="900"):
+            session.check_device_errors()
+        session.check_device_errors()               # reported once, then clear
+        out = session.generate([[1, 2, 3]], cb.GenerationOptions(max_new_tokens=2, stop_ids=[]))
+        assert len(out[0].tokens) == 2
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(8, 256, generator=g).to(torch.bfloat16); w = torch.randn(128, 256, generator=g).to(torch.bfloat16)
+    y = torch.empty(8, 128, device=DEV)
+    ops.gemm_tc(x.to(DEV), w.to(DEV), y)
+    close(y, x.double() @ w.double().t(), torch.float32)
+    with pytest.raises(cb.CitlaliError, match="one second"):
+        ops.wait_selftest(torch.zeros(4, dtype=torch.int32, device=DEV), limit_ms=5000.0)
+
+
 @pytest.mark.parametrize("inter,run", [(48, 16), (50, 50), (160, 16), (7, 1)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(inter, run, dtype):
