@@ -31,6 +31,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "tc_host.h"
 
 namespace citlali {
 namespace fatc {
@@ -461,41 +462,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (EncodeTiledFn)f;
-    }();
-    return fn;
-}
-
 // [rows, row_elems] bfloat16, row pitch `pitch_elems`, as boxes of [box_rows, 64] with 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_elems, uint64_t pitch_elems, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        set_last_error("attention_prefill_tc: the driver does not provide cuTensorMapEncodeTiled");
-        return kNoDriverEntry;
-    }
-    cuuint64_t dims[2] = {row_elems, rows};
-    cuuint64_t strides[1] = {pitch_elems * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("attention_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
-        return kBadShape;
-    }
-    return 0;
+    return tc::make_bf16_map(map, base, rows, row_elems, pitch_elems, box_rows, "attention_prefill_tc");
 }
 
 }  // namespace fatc

@@ -26,6 +26,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "tc_host.h"
 
 #include <cstdio>
 #include <map>
@@ -43,11 +44,6 @@ __host__ __device__ constexpr int epilogue_warps(bool swapped, int bn) { return 
 __host__ __device__ constexpr int threads_for(bool swapped, int bn) { return 64 + 32 * epilogue_warps(swapped, bn); }
 constexpr int kMaxSplits = 8;       // a cluster's portable size
 constexpr int kMaxSwappedRows = 256;
-
-enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
-
-// silu(g) * u with the fast exponential and the approximate division (a few ulp, before rounding to bfloat16)
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct GemmParams {
     void* out;             // [M, N] ([M, N / 2] under the gate epilogue)
@@ -244,117 +240,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
         // What becomes of 16 finished values: row i of the 128-row operand, rows j0 .. j0+15 of the other.
         auto finish = [&](const float (&v)[16], int i, int j0, int c0) {
-            if (p.out_kind == kSwigluBF16) {
-                // Weight rows alternate in runs of 16: gate rows, then the up rows of the same outputs.
+            if constexpr (!kSwapped) {
+                // i is a row m of x, j an output feature n
+                finish_rows(v, i, j0, c0, gate_keep, p.out, p.out_kind, p.M, p.N, epilogue_stage, lane, out_policy);
+            } else if (p.out_kind == kSwigluBF16) {
+                // i is an output feature n, j a row m of x.  Weight rows alternate in runs of 16 (gate rows, then the
+                // up rows of the same outputs): lanes 0-15 of a warp hold gate values, lanes 16-31 the matching up values
                 const int half_n = p.N >> 1;
-                if (kSwapped) {
-                    // lanes 0-15 of a warp hold gate values, lanes 16-31 the matching up values
-                    const int o_col = (i >> 5) * 16 + (lane & 15);
+                const int o_col = (i >> 5) * 16 + (lane & 15);
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v[c], 16);
-                        const int m = j0 + c;
-                        if ((lane & 16) == 0 && i < p.N && m < p.M)
-                            outh[(size_t)m * half_n + o_col] = __float2bfloat16_rn(silu_mul(v[c], other));
-                    }
-                } else if ((c0 & 16) == 0) {
-                    // this thread holds 16 consecutive columns: a gate run on even chunks, its up run on odd ones
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
-                } else if (j0 + 16 <= p.N && (half_n % 8) == 0) {
-                    // whole run: the warp writes its 32 rows x 16 outputs with full sectors
-                    uint32_t w[8];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
-                                                                  silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
-                        w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                    }
-                    const int row0 = i - lane;
-                    warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * half_n + ((j0 - 16) >> 1), (size_t)half_n, p.M - row0, lane, out_policy);
-                } else if (i < p.M && j0 - 16 < p.N) {
-                    const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
-                    if (j0 + 16 <= p.N && (half_n % 8) == 0) {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
-                                                                      silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
-                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c)
-                            if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
-                    }
+                for (int c = 0; c < 16; ++c) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[c], 16);
+                    const int m = j0 + c;
+                    if ((lane & 16) == 0 && i < p.N && m < p.M)
+                        outh[(size_t)m * half_n + o_col] = __float2bfloat16_rn(silu_mul(v[c], other));
                 }
-            } else if (kSwapped) {
-                // i is an output feature n, j a row m of x: out[m, n]; lanes hold consecutive n
-                if (i < p.N) {
+            } else if (i < p.N) {
+                // out[m, n]; lanes hold consecutive n
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int m = j0 + c;
-                        if (m < p.M) {
-                            const size_t o = (size_t)m * p.N + i;
-                            if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[c]);
-                            else if (p.out_kind == kAddF32) red_add_f32(outf + o, v[c]);
-                            else outf[o] = v[c];
-                        }
+                for (int c = 0; c < 16; ++c) {
+                    const int m = j0 + c;
+                    if (m < p.M) {
+                        const size_t o = (size_t)m * p.N + i;
+                        if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[c]);
+                        else if (p.out_kind == kAddF32) red_add_f32(outf + o, v[c]);
+                        else outf[o] = v[c];
                     }
-                }
-            } else if (p.out_kind == kStoreBF16 && j0 + 16 <= p.N && (p.N % 8) == 0) {
-                // i is a row m of x, j an output feature n; whole chunk: the warp writes 32 rows x 16 with full sectors
-                uint32_t w[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
-                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                const int row0 = i - lane;
-                warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, out_policy);
-            } else if (p.out_kind != kStoreBF16 && j0 + 16 <= p.N && (p.N % 4) == 0) {
-                const int row0 = i - lane;
-                warp_rows_out_f32(epilogue_stage, v, outf + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, p.out_kind == kAddF32, out_policy);
-            } else if (i < p.M && j0 < p.N) {
-                // i is a row m of x, j an output feature n: this thread holds 16 consecutive n
-                const size_t o = (size_t)i * p.N + j0;
-                const bool full = j0 + 16 <= p.N;
-                if (p.out_kind == kStoreBF16) {
-                    if (full && (p.N % 8) == 0) {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
-                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c)
-                            if (j0 + c < p.N) outh[o + c] = __float2bfloat16_rn(v[c]);
-                    }
-                } else if (full && (p.N % 4) == 0) {
-                    float4* dst = reinterpret_cast<float4*>(outf + o);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float4 t = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                        if (p.out_kind == kAddF32) {
-                            const float4 old = dst[c];
-                            t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
-                        }
-                        dst[c] = t;
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c)
-                        if (j0 + c < p.N) {
-                            if (p.out_kind == kAddF32) outf[o + c] += v[c]; else outf[o + c] = v[c];
-                        }
                 }
             }
         };
@@ -484,42 +395,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 // ---- host side ---------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (EncodeTiledFn)f;
-    }();
-    return fn;
-}
-
 // A [rows, K] bfloat16 row-major matrix as tiles of [box_rows, 64] with 128-byte swizzle;
 // outside the matrix a tile reads zeros.
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        set_last_error("gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
-        return kNoDriverEntry;
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("gemm_tc: cuTensorMapEncodeTiled failed with %d for a [%d, %d] matrix at %p", (int)r, rows, K, base);
-        return kBadShape;
-    }
-    return 0;
+    return make_bf16_map(map, base, (uint64_t)rows, (uint64_t)K, (uint64_t)K, box_rows, "gemm_tc");
 }
 
 struct Plan {

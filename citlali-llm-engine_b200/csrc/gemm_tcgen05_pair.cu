@@ -20,6 +20,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "tc_host.h"
 
 namespace citlali {
 namespace tc {
@@ -29,11 +30,6 @@ constexpr int kBM = 128, kBK = 64, kAccStages = 2;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kTmemCols = 512;
-
-enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
-
-// silu(g) * u with the fast exponential and the approximate division (a few ulp, before rounding to bfloat16)
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 struct Params {
     void* out;
@@ -147,99 +143,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
     } else {
         const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32 * quarter ..
-        float* outf = (float*)p.out;
-        __nv_bfloat16* outh = (__nv_bfloat16*)p.out;
         float gate_keep[16];
         const uint64_t out_policy = l2_evict_first_policy();
         wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
 
-        // What becomes of 16 finished values: row i of x, output features j0 .. j0+15.
         auto finish = [&](const float (&v)[16], int i, int j0, int c0) {
-            if (p.out_kind == kSwigluBF16) {
-                // Weight rows alternate in runs of 16: gate rows, then the up rows of the same outputs.
-                const int half_n = p.N >> 1;
-                if ((c0 & 16) == 0) {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
-                } else if (j0 + 16 <= p.N && (half_n % 8) == 0) {
-                    uint32_t w[8];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
-                                                                  silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
-                        w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                    }
-                    const int row0 = i - lane;
-                    warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * half_n + ((j0 - 16) >> 1), (size_t)half_n, p.M - row0, lane, out_policy);
-                } else if (i < p.M && j0 - 16 < p.N) {
-                    const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
-                    if (j0 + 16 <= p.N && (half_n % 8) == 0) {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
-                                                                      silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
-                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c)
-                            if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
-                    }
-                }
-            } else if (p.out_kind == kStoreBF16 && j0 + 16 <= p.N && (p.N % 8) == 0) {
-                uint32_t w[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
-                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                const int row0 = i - lane;
-                warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, out_policy);
-            } else if (p.out_kind != kStoreBF16 && j0 + 16 <= p.N && (p.N % 4) == 0) {
-                const int row0 = i - lane;
-                warp_rows_out_f32(epilogue_stage, v, outf + (size_t)row0 * p.N + j0, (size_t)p.N, p.M - row0, lane, p.out_kind == kAddF32, out_policy);
-            } else if (i < p.M && j0 < p.N) {
-                const size_t o = (size_t)i * p.N + j0;
-                const bool full = j0 + 16 <= p.N;
-                if (p.out_kind == kStoreBF16) {
-                    if (full && (p.N % 8) == 0) {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
-                            w[c] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(outh + o);
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c)
-                            if (j0 + c < p.N) outh[o + c] = __float2bfloat16_rn(v[c]);
-                    }
-                } else if (full && (p.N % 4) == 0) {
-                    float4* dst = reinterpret_cast<float4*>(outf + o);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float4 t = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                        if (p.out_kind == kAddF32) {
-                            const float4 old = dst[c];
-                            t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
-                        }
-                        dst[c] = t;
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c)
-                        if (j0 + c < p.N) {
-                            if (p.out_kind == kAddF32) outf[o + c] += v[c]; else outf[o + c] = v[c];
-                        }
-                }
-            }
+            finish_rows(v, i, j0, c0, gate_keep, p.out, p.out_kind, p.M, p.N, epilogue_stage, lane, out_policy);
         };
 
         const uint32_t leader_acc_empty0 = cluster_addr(smem_u32(&acc_empty_bar[0]), 0);
@@ -282,42 +191,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (EncodeTiledFn)f;
-    }();
-    return fn;
-}
-
 // A [rows, K] bfloat16 row-major matrix as tiles of [box_rows, 64] with 128-byte swizzle;
 // outside the matrix a tile reads zeros.
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        set_last_error("gemm_tc_pair: the driver does not provide cuTensorMapEncodeTiled");
-        return kNoDriverEntry;
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("gemm_tc_pair: cuTensorMapEncodeTiled failed with %d for a [%d, %d] matrix at %p", (int)r, rows, K, base);
-        return kBadShape;
-    }
-    return 0;
+    return make_bf16_map(map, base, (uint64_t)rows, (uint64_t)K, (uint64_t)K, box_rows, "gemm_tc_pair");
 }
 
 // The number of clusters of two that the device runs at once (not every SM has a partner free).
@@ -415,6 +292,6 @@ extern "C" int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y
     p.M = M; p.N = N; p.K = K;
     p.error_flag = error_flag;
     p.out = y;
-    p.out_kind = swiglu ? tc::pair::kSwigluBF16 : accumulate ? tc::pair::kAddF32 : (y_dtype == kF32 ? tc::pair::kStoreF32 : tc::pair::kStoreBF16);
+    p.out_kind = swiglu ? tc::kSwigluBF16 : accumulate ? tc::kAddF32 : (y_dtype == kF32 ? tc::kStoreF32 : tc::kStoreBF16);
     return N >= 256 ? tc::pair::launch<256>(x, w, p, stream) : tc::pair::launch<128>(x, w, p, stream);
 }

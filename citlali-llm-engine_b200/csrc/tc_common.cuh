@@ -258,5 +258,107 @@ __device__ __forceinline__ void warp_rows_out_bf16(uint32_t stage, const uint32_
     __syncwarp();
 }
 
+// ---- what a product kernel's epilogue does with its values (rows of x on the tensor memory's lanes) ----------
+
+enum OutKind : int { kStoreBF16 = 0, kStoreF32 = 1, kAddF32 = 2, kSwigluBF16 = 4 };
+
+// silu(g) * u with the fast exponential and the approximate division (a few ulp, before rounding to bfloat16)
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// 16 finished values of row i of x, output features j0 .. j0+15 (c0 = j0 within the tile), of a product
+// y[M, N]: stored as bfloat16 or float32, added to float32, or, under the gate epilogue, kept (a gate run, even
+// chunks) and then combined with the up run that follows into y[M, N/2] = silu(gate) * up.  Whole chunks of
+// whole 32-row groups leave through the warp's area at `epilogue_stage` so that every store covers whole sectors.
+__device__ __forceinline__ void finish_rows(const float (&v)[16], int i, int j0, int c0, float (&gate_keep)[16], void* out,
+                                            int out_kind, int M, int N, uint32_t epilogue_stage, int lane, uint64_t out_policy) {
+    float* outf = (float*)out;
+    __nv_bfloat16* outh = (__nv_bfloat16*)out;
+    if (out_kind == kSwigluBF16) {
+        // Weight rows alternate in runs of 16: gate rows, then the up rows of the same outputs.
+        const int half_n = N >> 1;
+        if ((c0 & 16) == 0) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) gate_keep[c] = v[c];
+        } else if (j0 + 16 <= N && (half_n % 8) == 0) {
+            uint32_t w[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                          silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                w[c] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            const int row0 = i - lane;
+            warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * half_n + ((j0 - 16) >> 1), (size_t)half_n, M - row0, lane, out_policy);
+        } else if (i < M && j0 - 16 < N) {
+            const size_t o = (size_t)i * half_n + ((j0 - 16) >> 1);
+            if (j0 + 16 <= N && (half_n % 8) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(gate_keep[2 * c], v[2 * c]),
+                                                              silu_mul(gate_keep[2 * c + 1], v[2 * c + 1]));
+                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    if (((j0 - 16) >> 1) + c < half_n) outh[o + c] = __float2bfloat16_rn(silu_mul(gate_keep[c], v[c]));
+            }
+        }
+    } else if (out_kind == kStoreBF16 && j0 + 16 <= N && (N % 8) == 0) {
+        uint32_t w[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+            w[c] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        const int row0 = i - lane;
+        warp_rows_out_bf16(epilogue_stage, w, outh + (size_t)row0 * N + j0, (size_t)N, M - row0, lane, out_policy);
+    } else if (out_kind != kStoreBF16 && j0 + 16 <= N && (N % 4) == 0) {
+        const int row0 = i - lane;
+        warp_rows_out_f32(epilogue_stage, v, outf + (size_t)row0 * N + j0, (size_t)N, M - row0, lane, out_kind == kAddF32, out_policy);
+    } else if (i < M && j0 < N) {
+        const size_t o = (size_t)i * N + j0;
+        const bool full = j0 + 16 <= N;
+        if (out_kind == kStoreBF16) {
+            if (full && (N % 8) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * c], v[2 * c + 1]);
+                    w[c] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(outh + o);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    if (j0 + c < N) outh[o + c] = __float2bfloat16_rn(v[c]);
+            }
+        } else if (full && (N % 4) == 0) {
+            float4* dst = reinterpret_cast<float4*>(outf + o);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float4 t = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                if (out_kind == kAddF32) {
+                    const float4 old = dst[c];
+                    t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+                }
+                dst[c] = t;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+                if (j0 + c < N) {
+                    if (out_kind == kAddF32) outf[o + c] += v[c]; else outf[o + c] = v[c];
+                }
+        }
+    }
+}
+
 }  // namespace tc
 }  // namespace citlali
