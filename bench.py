@@ -12,7 +12,6 @@ step's tokens coming from pinned host memory and the sampled tokens read back ev
 must read; ``points`` give decode at batch 1 and 64.  Several GPUs are not supported.
 """
 import argparse
-import dataclasses
 import json
 import os
 import random

@@ -25,7 +25,7 @@ Interfaces (all tensors are on the model's device; ``x`` is the float32 residual
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional
+from typing import Dict, List, Optional
 
 import torch
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, Iterable, Optional, Sequence
+from typing import Dict, Sequence
 
 import torch
 

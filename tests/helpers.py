@@ -1,6 +1,4 @@
 """Tiny configurations and small utilities shared by the tests."""
-import json
-import os
 import random
 
 import torch

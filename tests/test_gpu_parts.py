@@ -1,6 +1,5 @@
 """Each part alone, built through the registries with sizes the models do not use, against the
 plain implementation's function for that part."""
-import math
 
 import pytest
 import torch

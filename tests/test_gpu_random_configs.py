@@ -5,7 +5,6 @@ three tokens each one by one, in 32-bit and in bfloat16, against the plain imple
 import random
 
 import pytest
-import torch
 
 import citlali_b200 as cb
 import plain_qwen3 as plain

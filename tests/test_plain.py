@@ -1,7 +1,6 @@
 """The plain implementation checked against itself and against elementary identities."""
 import math
 
-import pytest
 import torch
 
 import plain_qwen3 as plain

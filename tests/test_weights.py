@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import citlali_b200 as cb
-from helpers import SEEDS, TINY, make_model_dir, tiny_config
+from helpers import SEEDS, make_model_dir, tiny_config
 
 
 def test_safetensors_round_trip_agrees_with_the_safetensors_package(tmp_path):

@@ -15,7 +15,6 @@ import random
 import pytest
 import torch
 
-import citlali_b200 as cb
 from citlali_b200 import ops
 
 pytestmark = pytest.mark.gpu
