@@ -7,7 +7,7 @@ Kept from the reference with their names, defaults and meaning (main.cpp:203-247
 (main.cpp:149-157).  The reference's ``--prompt`` takes text; there is no tokenizer here, so
 prompts are token ids: ``--prompt-ids 1,2,3`` (repeat it for a batch) or ``--prompt-file``
 (a JSON list of lists).  Text modes, quantized residency and remote offload have no
-counterpart.  Added: ``--temperature``, ``--seed``, ``--stop-ids``, ``--dtype``, ``--slots``,
+counterpart: their options are refused with the reason.  Added: ``--temperature``, ``--seed``, ``--stop-ids``, ``--dtype``, ``--slots``,
 ``--json``, ``--random-weights SEED``.
 """
 from __future__ import annotations
@@ -36,6 +36,17 @@ USAGE = """usage: citlali_cli --model <dir> (--prompt-ids 1,2,3 [--prompt-ids ..
   --json                   print results as one JSON object
   --help, -h               this text
 """
+
+
+# options of the reference's command line (main.cpp:203-247) that have no counterpart here, and why
+_NO_TOKENIZER = "this library has no tokenizer; give token ids with --prompt-ids 1,2,3 or --prompt-file <json>"
+_NO_OFFLOAD = "quantized residency and remote offload are not part of this library"
+REFERENCE_ONLY = {
+    "--prompt": _NO_TOKENIZER, "--tokens": _NO_TOKENIZER, "--interactive": _NO_TOKENIZER,
+    "--no-chat-template": _NO_TOKENIZER,
+    "--quantized": _NO_OFFLOAD, "--offload": _NO_OFFLOAD, "--remote": _NO_OFFLOAD, "--remote-backend": _NO_OFFLOAD,
+    "--remote-transport": _NO_OFFLOAD,
+}
 
 
 @dataclass
@@ -107,6 +118,8 @@ def parse_args(argv: List[str]) -> CliArgs:
             args.json = True
         elif arg in ("--help", "-h"):
             args.help = True
+        elif arg in REFERENCE_ONLY:
+            raise RuntimeError(f"{arg}: {REFERENCE_ONLY[arg]}")
         else:
             raise RuntimeError("unknown argument: " + arg)
         i += 1
