@@ -60,7 +60,10 @@ def peaks():
         try:
             with open(path) as f:
                 d = json.load(f)
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            pk = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:          # a seconds-long loop under the power cap
+                pk["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return pk
         except Exception:
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
@@ -282,6 +285,8 @@ def main():
     prefill_flops = 2.0 * T * layer_params * layers + 2.0 * H * vocab + layers * 4.0 * (T * (T + 1) / 2) * d * nq
     prefill = {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
                "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "tflops": prefill_flops / (prefill_ms / 1e3) / 1e12}
+    if "bf16_tflops_sustained" in pk:
+        prefill["frac_sustained"] = prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---- decode -----------------------------------------------------------------------------
