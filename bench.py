@@ -16,6 +16,7 @@ import json
 import os
 import random
 import re
+import shutil
 import statistics
 import subprocess
 import sys
@@ -154,6 +155,107 @@ def run_workload(index, repetitions):
     return 0
 
 
+def run_reference(args):
+    """The unmodified reference (built under baseline/_ref by ``baseline/reference_arm.py install``) at the
+    benchmark's sizes: it serves ONE sequence, token by token, in FP16, so its line is decode at batch 1 near
+    the context length; batches of 8 and 64 and a one-step prompt have no counterpart in it
+    (src/runtime/session.cpp:69-74: the prompt is a loop over forward_token)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    try:
+        import reference_arm
+    except Exception as e:
+        return unavailable(f"baseline/reference_arm.py cannot be imported: {e}")
+    why = reference_arm.installed()
+    if why and os.path.isdir("/root/reference"):
+        try:
+            reference_arm.install("/root/reference")
+            why = reference_arm.installed()
+        except Exception as e:
+            why = f"the reference could not be built here: {str(e)[-300:]}"
+    if why:
+        return unavailable(why)
+    if args.gpus != 1:
+        return unavailable("the reference runs one sequence on one GPU; several GPUs have no meaning for it")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device here; the reference has no CPU path")
+    except Exception as e:
+        return unavailable(f"torch is needed to make the random model file: {e}")
+    shape = benchmark_shape()
+    layers_full = shape["num_hidden_layers"]
+    layers = args.layers or layers_full
+    context = shape["context"]
+    K, W = args.steps, max(args.warmup, 3)
+    config = dict(num_hidden_layers=layers, hidden_size=shape["hidden_size"], num_attention_heads=shape["num_attention_heads"],
+                  num_key_value_heads=shape["num_key_value_heads"], head_dim=shape["head_dim"],
+                  intermediate_size=shape["intermediate_size"], vocab_size=shape["vocab_size"], rope_theta=shape["rope_theta"],
+                  rms_norm_eps=shape["rms_norm_eps"], tie_word_embeddings=shape["tie_word_embeddings"],
+                  max_position_embeddings=context)
+    need = 2 * (layers * ((shape["num_attention_heads"] * 2 + shape["num_key_value_heads"] * 2) * shape["head_dim"]
+                          * shape["hidden_size"] + 3 * shape["hidden_size"] * shape["intermediate_size"])
+                + 2 * shape["vocab_size"] * shape["hidden_size"]) + (64 << 20)
+    folder = None
+    for base in (tempfile.gettempdir(), "/dev/shm"):
+        try:
+            if os.path.isdir(base) and shutil.disk_usage(base).free > need * 1.1:
+                folder = tempfile.mkdtemp(prefix="citlali_reference_", dir=base)
+                break
+        except OSError:
+            continue
+    if folder is None:
+        return unavailable(f"no temporary folder has the {need / 1e9:.0f} GB that the reference's model file needs")
+    gguf = os.path.join(folder, "model.gguf")
+    clocks = ClockSampler()
+    try:
+        t0 = time.time()
+        size = reference_arm.gguf_random(config, gguf, seed=1, device="cuda:0",
+                                         progress=lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True))
+        torch.cuda.empty_cache()
+        print(f"[bench] reference arm: model file of {size / 1e9:.1f} GB written in {time.time() - t0:.0f} s",
+              file=sys.stderr, flush=True)
+        start = context - (1 + W + K)
+        clocks.start()
+        r = reference_arm.reference_decode(gguf, context, 1, W, K, start_position=start)
+        clock_record = clocks.stop()
+    except Exception as e:
+        clocks.stop()
+        return unavailable(f"the reference did not run: {str(e)[-300:]}")
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    print(f"[bench] reference arm: {r}", file=sys.stderr, flush=True)
+    pk = peaks()
+    kv_bytes_per_token = 2 * shape["num_key_value_heads"] * shape["head_dim"] * 2 * layers
+    mean_len = (r["first_timed_position"] + r["last_timed_position"]) / 2.0 + 1
+    step_bytes = need - (64 << 20) - 2 * shape["vocab_size"] * shape["hidden_size"] + mean_len * kv_bytes_per_token
+    achieved = step_bytes / (r["ms_per_step"] / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "decode tok/s @ batch 1 (Qwen3-8B shape, random fp16 weights): the reference serves one sequence",
+        "value": r["tokens_per_second"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic: random weights N(0,0.02) in a GGUF file, token ids from its own greedy loop",
+        "impl": "reference",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": layers_full, "hidden": shape["hidden_size"],
+                   "q_heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+                   "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+                   "global_batch": 1, "seq_len": context, "first_timed_position": r["first_timed_position"],
+                   "parallelism": "single GPU", "compare_with": "points.decode_b1 of the other arm",
+                   "no_counterpart": "batch 8 and 64, a one-step prompt (its prompt is a loop over single tokens)",
+                   "timing": "host clock around QwenModel::forward_token, which synchronises the device every token",
+                   "cache_below_start": "as allocated: its kernels' work depends on the position alone",
+                   "peaks": pk["source"]},
+        "e2e": {"value": r["tokens_per_second"], "unit": "tok/s", "h2d_bytes_per_step": 4,
+                "d2h_bytes_per_step": 4 * shape["vocab_size"],
+                "note": "forward_token is the reference's end-to-end step: token id in, all logits copied to the host, argmax there"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+        "load_seconds": r["load_seconds"], "clocks": clock_record}))
+    return 0
+
+
 class ClockSampler:
     """nvidia-smi in the background while something is timed."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -218,10 +320,7 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake/C++ project with no Python package to install (no setup.py or "
-                          "pyproject.toml), cannot batch, and has no safetensors, bfloat16 or prefill path"}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2

@@ -1,16 +1,21 @@
 """A plain, slow implementation of the Qwen3 dense decoder: the tests' oracle.
 
-It rests on the reference's formulas only.  The reference's model code cannot run on a
-CPU (every op is a CUDA kernel and every weight goes through cudaMalloc,
-src/compute/cuda/tensor.cu:56), so nothing here was compared with its output; each
-function cites the reference lines it restates.  Whole sequences, no cache, one function
-per part, no code shared with the engine: it reads the model folder with the ``safetensors``
-package and ``json``, and computes with elementary torch operations on the CPU.
+Each function restates one formula of the reference and cites its lines.  The reference's model
+code cannot run on a CPU (every op is a CUDA kernel and every weight goes through cudaMalloc,
+src/compute/cuda/tensor.cu:56), but it builds unmodified for sm_100a and runs on a B200: its own
+logits for four tiny random models are stored under ``tests/golden/`` (made by
+``tests/golden/make_golden.py``), and ``tests/test_golden_reference.py`` holds this file to them on
+the CPU, to 1.4e-3 of the largest logit as it stands (the reference's FP16 stores) and to 8e-4 when
+this oracle rounds to FP16 where the reference does (``reference_model_logits``).
+
+Whole sequences, no cache, one function per part, no code shared with the engine: it reads the
+model folder with the ``safetensors`` package and ``json``, and computes with elementary torch
+operations on the CPU.
 
 All arithmetic runs in ``dtype`` (float64 by default, which makes the result the exact
 value of the formulas up to ~1e-15; float32 is there to see what 32-bit evaluation in
 another order gives).  The reference rounds to 16 bits at every store
-(src/compute/cuda/kernels.cu:13-24); an exact oracle leaves that out.
+(src/compute/cuda/kernels.cu:13-24); the exact oracle leaves that out, ``store_float16`` puts it in.
 """
 import json
 import math
@@ -117,37 +122,54 @@ def swiglu(gate, up):
     return gate / (1.0 + torch.exp(-gate)) * up
 
 
-def attention_block(h, w, prefix, cfg, positions):
+def keep(t):
+    """No rounding at a store: what the exact oracle does."""
+    return t
+
+
+def store_float16(t):
+    """The reference's rounding at every store of an activation: its buffers hold FP16 bits and each
+    kernel widens, computes in float and rounds once (kernels.cu:13-24).  With this as ``store`` (and
+    weights rounded to FP16, src/model/weight_loader.cpp:457-459) the oracle follows the reference's
+    own arithmetic; the scores and the logits stay unrounded as there (kernels.cu:599, :452-471)."""
+    return t.to(torch.float16).to(t.dtype)
+
+
+def attention_block(h, w, prefix, cfg, positions, store=keep):
     """q, k, v projections; q_norm and k_norm per head before the rotation; v untouched;
-    attention; output projection (qwen_model.cpp:315-351)."""
+    attention; output projection (qwen_model.cpp:315-351).  ``store`` is applied wherever the
+    reference writes a buffer: after each projection, each head norm, the rotation, the attention
+    output and the output projection."""
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
     T = h.shape[0]
-    q = linear(h, w[f"{prefix}.q_proj.weight"]).view(T, nq, d)
-    k = linear(h, w[f"{prefix}.k_proj.weight"]).view(T, nkv, d)
-    v = linear(h, w[f"{prefix}.v_proj.weight"]).view(T, nkv, d)
-    q = head_rms_norm(q, w[f"{prefix}.q_norm.weight"], eps)
-    k = head_rms_norm(k, w[f"{prefix}.k_norm.weight"], eps)
-    q = rotary_half_split(q, positions, cfg["rope_theta"])
-    k = rotary_half_split(k, positions, cfg["rope_theta"])
-    o = causal_attention(q, k, v, nq, nkv).reshape(T, nq * d)
-    return linear(o, w[f"{prefix}.o_proj.weight"])
+    q = store(linear(h, w[f"{prefix}.q_proj.weight"])).view(T, nq, d)
+    k = store(linear(h, w[f"{prefix}.k_proj.weight"])).view(T, nkv, d)
+    v = store(linear(h, w[f"{prefix}.v_proj.weight"])).view(T, nkv, d)
+    q = store(head_rms_norm(q, w[f"{prefix}.q_norm.weight"], eps))
+    k = store(head_rms_norm(k, w[f"{prefix}.k_norm.weight"], eps))
+    q = store(rotary_half_split(q, positions, cfg["rope_theta"]))
+    k = store(rotary_half_split(k, positions, cfg["rope_theta"]))
+    o = store(causal_attention(q, k, v, nq, nkv)).reshape(T, nq * d)
+    return store(linear(o, w[f"{prefix}.o_proj.weight"]))
 
 
-def feed_forward(h, w, prefix):
+def feed_forward(h, w, prefix, store=keep):
     """gate and up projections, SiLU gate, down projection (qwen_model.cpp:360-370)."""
-    g = linear(h, w[f"{prefix}.gate_proj.weight"])
-    u = linear(h, w[f"{prefix}.up_proj.weight"])
-    return linear(swiglu(g, u), w[f"{prefix}.down_proj.weight"])
+    g = store(linear(h, w[f"{prefix}.gate_proj.weight"]))
+    u = store(linear(h, w[f"{prefix}.up_proj.weight"]))
+    return store(linear(store(swiglu(g, u)), w[f"{prefix}.down_proj.weight"]))
 
 
-def decoder_layer(x, w, i, cfg, positions):
-    """norm -> attention -> x += ; norm -> feed-forward -> x += (qwen_model.cpp:306-374)."""
+def decoder_layer(x, w, i, cfg, positions, store=keep):
+    """norm -> attention -> x += ; norm -> feed-forward -> x += (qwen_model.cpp:306-374).  The
+    reference's residual stream is a 16-bit buffer too (kernels.cu:53-59): the sums are stored."""
     base = f"model.layers.{i}"
     eps = cfg["rms_norm_eps"]
-    x = x + attention_block(rms_norm(x, w[f"{base}.input_layernorm.weight"], eps), w,
-                            f"{base}.self_attn", cfg, positions)
-    x = x + feed_forward(rms_norm(x, w[f"{base}.post_attention_layernorm.weight"], eps), w, f"{base}.mlp")
+    x = store(x + attention_block(store(rms_norm(x, w[f"{base}.input_layernorm.weight"], eps)), w,
+                                  f"{base}.self_attn", cfg, positions, store))
+    x = store(x + feed_forward(store(rms_norm(x, w[f"{base}.post_attention_layernorm.weight"], eps)), w,
+                               f"{base}.mlp", store))
     return x
 
 
@@ -156,7 +178,7 @@ def head_weight(w):
     return w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
 
 
-def model_logits(cfg, w, tokens, dtype=torch.float64):
+def model_logits(cfg, w, tokens, dtype=torch.float64, store=keep):
     """Logits [T, vocab] at every position of one whole sequence (qwen_model.cpp:239-414):
     embedding, the layers, final norm, output matrix with no bias and no scaling."""
     w = {k: v.to(dtype) for k, v in w.items()}
@@ -164,9 +186,16 @@ def model_logits(cfg, w, tokens, dtype=torch.float64):
     positions = list(range(T))
     x = embedding(w["model.embed_tokens.weight"], tokens)
     for i in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, w, i, cfg, positions)
-    h = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+        x = decoder_layer(x, w, i, cfg, positions, store)
+    h = store(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     return linear(h, head_weight(w))
+
+
+def reference_model_logits(cfg, w, tokens):
+    """The oracle run the reference's way: weights rounded to FP16 as its loader stores them, every
+    activation rounded to FP16 where it writes a buffer."""
+    w16 = {k: v.to(torch.float16).to(torch.float64) for k, v in w.items()}
+    return model_logits(cfg, w16, tokens, torch.float64, store_float16)
 
 
 # ---- sampling and the generation loop --------------------------------------------------
