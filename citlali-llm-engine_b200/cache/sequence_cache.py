@@ -50,7 +50,7 @@ class KVGroup:
     requirement: KVRequirement
     steps: List[int]
     pages: PageAllocator
-    table_host: torch.Tensor          # [slots, max_pages] int32 (pinned when on a CUDA device)
+    table_host: torch.Tensor          # [slots, max_pages] int32, the host's record
     table: torch.Tensor               # the same on the device
     keys: torch.Tensor                # [layers, pages, kv_heads, page_size, head_dim]
     values: torch.Tensor
@@ -109,11 +109,11 @@ class SequenceCache:
                 by_state.setdefault(req, []).append(step)
             else:
                 raise CitlaliError(f"schedule step {step} asks for a cache of unknown kind {type(req).__name__}")
-        pin = self.device.type == "cuda"
+        self._pin = self.device.type == "cuda"
         self._has_window = any(req.window is not None for req in by_kv)
         for req, steps in by_kv.items():
             shape = (len(steps), self.num_pages, req.num_kv_heads, page_size, req.head_dim)
-            table_host = torch.zeros((num_slots, self.max_pages_per_slot), dtype=torch.int32, pin_memory=pin)
+            table_host = torch.zeros((num_slots, self.max_pages_per_slot), dtype=torch.int32)
             group = KVGroup(req, steps, PageAllocator(self.num_pages), table_host,
                             torch.zeros_like(table_host, device=self.device),
                             torch.zeros(shape, dtype=dtype, device=self.device),
@@ -178,7 +178,14 @@ class SequenceCache:
                 g.held[slot][i] = page
                 g.table_host[slot, i] = page
             lo, hi = missing[0], missing[-1] + 1
-            g.table[slot, lo:hi].copy_(g.table_host[slot, lo:hi], non_blocking=True)
+            # The host runs ahead of the device, and a slot given back may be taken again before an
+            # earlier step has run: every update travels in a pinned buffer of its own (the pinned
+            # allocator hands a buffer out again only after the copy from it is done), so a copy
+            # still queued never sees a later step's entries.
+            stage = g.table_host[slot, lo:hi].clone()
+            if self._pin:
+                stage = stage.pin_memory()
+            g.table[slot, lo:hi].copy_(stage, non_blocking=True)
 
     def commit(self, slot: int, new_length: int) -> None:
         """The step that wrote positions below ``new_length`` has been issued."""

@@ -178,7 +178,10 @@ attention_decode_combine_kernel(const float* __restrict__ partial, int max_chunk
     const int head = blockIdx.x, row = blockIdx.y;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int c0 = lo / chunk_keys, c1 = pos / chunk_keys, n = c1 - c0 + 1;
+    // positions are below the launch's max_positions by contract (the host checks every step); a
+    // position beyond it is clamped so that at least no partial is read that no block wrote
+    const int c1 = min(pos / chunk_keys, max_chunks - 1);
+    const int c0 = min(lo / chunk_keys, c1), n = c1 - c0 + 1;
     const float* base = partial + (((size_t)row * nq + head) * max_chunks + c0) * (d + 2);
     if (threadIdx.x < 32) {
         float M = -INFINITY;
@@ -607,6 +610,12 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
     const int chunk_keys = kChunkPages * page_size;
     const int max_chunks = (max_positions + chunk_keys - 1) / chunk_keys;
     const size_t need = (size_t)rows * nq * max_chunks * (head_dim + 2);
+    if ((size_t)(max_chunks + 1) * sizeof(float) > 48 * 1024) {
+        // the merge kernel keeps one weight per chunk in shared memory
+        set_last_error("attention_decode: %d positions in pages of %d are %d chunks, more than the merge kernel's %d",
+                       max_positions, page_size, max_chunks, 48 * 1024 / 4 - 1);
+        return kTooLarge;
+    }
     if (partial == nullptr || partial_floats < need) {
         set_last_error("attention_decode: %zu floats of scratch are needed, %zu were given", need, partial_floats);
         return kTooLarge;

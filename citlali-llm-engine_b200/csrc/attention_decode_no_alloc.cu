@@ -9,6 +9,8 @@
 #include "api.h"
 #include "common.cuh"
 
+#include <atomic>
+
 namespace citlali {
 
 static __device__ __align__(256) float g_no_alloc_scratch[CITLALI_NO_ALLOC_SCRATCH_FLOATS];
@@ -20,7 +22,10 @@ __global__ void no_alloc_scratch_anchor(float* out) {
 }
 
 constexpr int kMaxDevices = 64;
-static float* g_scratch_address[kMaxDevices] = {nullptr};
+// One address per device.  Two host threads that make their first call on a device at the same time
+// both look the address up and both store the same value: harmless, and the slot is atomic so that
+// neither reads a torn pointer.
+static std::atomic<float*> g_scratch_address[kMaxDevices];
 
 // The device address of the array on the current device; looked up on the first call per device.
 static int scratch_for_current_device(float** ptr) {
@@ -31,7 +36,8 @@ static int scratch_for_current_device(float** ptr) {
         set_last_error("attention_decode_no_alloc: device index %d is outside 0..%d", device, kMaxDevices - 1);
         return kBadShape;
     }
-    if (g_scratch_address[device] == nullptr) {
+    float* known = g_scratch_address[device].load(std::memory_order_acquire);
+    if (known == nullptr) {
         float* address = nullptr;
         e = cudaGetSymbolAddress((void**)&address, g_no_alloc_scratch);
         if (e != cudaSuccess) {
@@ -39,9 +45,10 @@ static int scratch_for_current_device(float** ptr) {
                            cudaGetErrorString(e));
             return (int)e;
         }
-        g_scratch_address[device] = address;
+        g_scratch_address[device].store(address, std::memory_order_release);
+        known = address;
     }
-    *ptr = g_scratch_address[device];
+    *ptr = known;
     return 0;
 }
 

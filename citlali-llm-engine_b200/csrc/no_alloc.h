@@ -23,7 +23,9 @@
 //
 //   First call.  The first call on each device looks up the array's device address
 //   (cudaGetSymbolAddress) and remembers it.  Make that first call outside any stream
-//   capture, with the device that will run the kernels current.
+//   capture, with the device that will run the kernels current.  Host threads may make their
+//   first calls at the same time: each looks the same address up, and the slot that keeps it is
+//   atomic.
 //
 //   Sharing.  All calls on a device share the one array, and it keeps whatever the last call
 //   left in it.  Nothing in it has to start at zero: every partial a call reads was written by

@@ -7,8 +7,13 @@ device buffers of fixed address: the tokens, each row's slot and position, the s
 parameters, the page tables.  The host fills a pinned mirror, issues one copy, and replays.
 
 A model can be replayed only if none of its parts looks at the host-side lists of a step
-(slots, lengths): parts say so with ``graph_safe = True``; for other models the session
-keeps stepping without graphs.
+(slots, lengths): every part answers for itself, once bound, with ``graph_safe`` (an attention
+part says yes only for the dtype and head size whose single-token kernel reads positions on the
+device); for other models the session keeps stepping without graphs.
+
+The host runs ahead of the device: ``launch`` returns before the replay has run.  A pinned mirror
+must therefore not be rewritten while a copy from it may still be pending; the mirrors form a ring,
+and each waits for the event recorded behind its last copy before it is written again.
 """
 from __future__ import annotations
 
@@ -22,13 +27,35 @@ from ..parts.base import StepBatch
 
 
 def model_is_graph_safe(model) -> bool:
-    if model.ctx.dtype != torch.bfloat16:
-        return False          # the 32-bit attention kernel sizes its shared memory from the lengths
+    """Every part of every layer, as bound, steps from device memory alone."""
     for block in model.layers:
         for part in block.parts():
             if not getattr(part, "graph_safe", False):
                 return False
     return True
+
+
+class _PinnedRing:
+    """A few pinned host buffers of one shape used in turn.  ``next()`` hands out the buffer whose last
+    copy is longest ago, after waiting for that copy; ``sent(stream)`` marks the copy just issued."""
+
+    def __init__(self, shape, dtype, depth: int = 4):
+        self.buffers = [torch.zeros(shape, dtype=dtype, pin_memory=True) for _ in range(depth)]
+        self.events = [None] * depth
+        self.at = -1
+
+    def next(self) -> torch.Tensor:
+        self.at = (self.at + 1) % len(self.buffers)
+        ev = self.events[self.at]
+        if ev is not None:
+            ev.synchronize()
+        return self.buffers[self.at]
+
+    def sent(self) -> None:
+        ev = self.events[self.at]
+        if ev is None:
+            ev = self.events[self.at] = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
 
 
 class DecodeGraphRunner:
@@ -43,10 +70,9 @@ class DecodeGraphRunner:
         self._offsets = [0]
         for s in self._sizes:
             self._offsets.append(self._offsets[-1] + (s + 3) // 4 * 4)
-        self.ints_host = torch.zeros(self._offsets[-1], dtype=torch.int32, pin_memory=True)
-        self._ints_np = self.ints_host.numpy()           # the same pinned memory, written without tensor ops
+        self.ints_ring = _PinnedRing((self._offsets[-1],), torch.int32)
         self.ints = torch.zeros(self._offsets[-1], dtype=torch.int32, device=dev)
-        self.floats_host = torch.zeros((2, B), dtype=torch.float32, pin_memory=True)   # temperature, uniform
+        self.floats_ring = _PinnedRing((2, B), torch.float32)                           # temperature, uniform
         self.floats = torch.zeros((2, B), dtype=torch.float32, device=dev)
         self.out_tokens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.out_host = torch.zeros(B, dtype=torch.int32, pin_memory=True)
@@ -54,11 +80,11 @@ class DecodeGraphRunner:
         self.logits: Dict[Tuple[int, bool], torch.Tensor] = {}
         self.kernels_per_replay: Dict[Tuple[int, bool], int] = {}
         self._pool = None
-        # constant parts of the mirror: one row per sequence
-        seq_start = self._piece(self.ints_host, 3, B + 1)
-        seq_start.copy_(torch.arange(B + 1, dtype=torch.int32))
-        self._piece(self.ints_host, 6, B).copy_(torch.arange(B, dtype=torch.int32))
-        self.ints.copy_(self.ints_host)
+        # constant parts, in every mirror and on the device: one row per sequence
+        for host in self.ints_ring.buffers:
+            self._piece(host, 3, B + 1).copy_(torch.arange(B + 1, dtype=torch.int32))
+            self._piece(host, 6, B).copy_(torch.arange(B, dtype=torch.int32))
+        self.ints.copy_(self.ints_ring.buffers[0])
 
     def _piece(self, buf, i, n):
         return buf[self._offsets[i]:self._offsets[i] + n]
@@ -104,7 +130,8 @@ class DecodeGraphRunner:
         """Write the step's inputs into the pinned mirror and issue the copies.  ``tokens`` None:
         keep the device's token buffer (fed from the last step's output on the device)."""
         n = len(slots)
-        h, o = self._ints_np, self._offsets
+        host = self.ints_ring.next()
+        h, o = host.numpy(), self._offsets               # the same pinned memory, written without tensor ops
         if tokens is not None:
             h[o[0]:o[0] + n] = tokens
         h[o[1]:o[1] + n] = slots
@@ -113,16 +140,20 @@ class DecodeGraphRunner:
         h[o[5]:o[5] + n] = positions
         lo = 0 if tokens is not None else o[1]
         hi = o[6]
-        self.ints[lo:hi].copy_(self.ints_host[lo:hi], non_blocking=True)
+        self.ints[lo:hi].copy_(host[lo:hi], non_blocking=True)
+        self.ints_ring.sent()
         if temperature > 0.0:
-            self.floats_host[0, :n] = float(temperature)
-            self.floats_host[1, :n] = torch.as_tensor(list(uniforms), dtype=torch.float32)
-            self.floats.copy_(self.floats_host, non_blocking=True)
+            fh = self.floats_ring.next()
+            fh[0, :n] = float(temperature)
+            fh[1, :n] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+            self.floats.copy_(fh, non_blocking=True)
+            self.floats_ring.sent()
 
     def launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]], temperature: float,
                uniforms: Sequence[float]) -> int:
         """Reserve cache room, copy the inputs, replay the graph, advance the lengths.  Returns the
-        number of kernels the replay launched.  Nothing is synchronised."""
+        number of kernels the replay launched.  Nothing is synchronised: steps may be issued back to
+        back, each step's inputs travel in a pinned buffer no later step touches until its copy is done."""
         n = len(slots)
         require(0 < n <= self.max_batch, f"{n} sequences exceed the runner's {self.max_batch}")
         positions = [self.cache.length(s) for s in slots]

@@ -78,7 +78,7 @@ class DecoderModel:
             tie = spec.head_name not in weights      # absent head: reuse the embedding (qwen_model.cpp:71-75)
         self.tied = bool(tie)
         if self.tied:
-            self.head.bind_shared(self.embedding, ctx.dtype)
+            self.head.bind_shared(self.embedding, ctx)
         else:
             require(spec.head_name in weights, f"missing required tensor: {spec.head_name}")
             self.head.bind(weights, ctx)

@@ -127,7 +127,10 @@ class InferenceSession:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the given tokens of every entry as one batch from the cache; return float32 logits
         ``[wanted, vocab]`` on the device, in the order of the entries and of their ``want``.
-        The entries' sequences either all start or all continue; their lengths may differ."""
+        Every entry appends its tokens to its slot, whatever the slot holds: sequences that start,
+        sequences that go on by one token and sequences that go on by several may share a step, and
+        their lengths may differ.  A step in which every entry brings one token runs the single-token
+        kernels; any other step runs the ones for runs of tokens."""
         require(self.model is not None, "no model is loaded")
         entries = list(entries)
         require(len(entries) > 0, "a step needs at least one entry")
@@ -138,9 +141,6 @@ class InferenceSession:
             require(p + len(e.tokens) <= self.max_context,
                     f"slot {e.slot}: {p} cached + {len(e.tokens)} new tokens exceed max_context {self.max_context}")
             past.append(p)
-        starting = [p == 0 for p in past]
-        require(all(starting) or not any(starting),
-                "the sequences of a step either all start or all continue; no request joins a running batch")
         batch = pack_step(entries, past, self.model.spec.vocab_size, self.model.ctx.device)
         for e, p in zip(entries, past):
             self.cache.reserve(e.slot, p + len(e.tokens))

@@ -175,16 +175,25 @@ def sample_rows(logits, temperature, uniform, tokens):
 
 # ---- choices between kernels ---------------------------------------------------------------
 
+def attention_steps_from_device(dtype, head_dim: int) -> bool:
+    """Whether a step of single tokens in this dtype and head size runs the split-context kernel, whose
+    launch depends on no host-side length (the condition :func:`attention` tests first)."""
+    return dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256
+
+
 def attention(q, q_stride, cache_view, batch, out, nq, nkv, head_dim, window, scale):
     """Attention of every row of the step over its slot's cache.  ``q`` holds the rotated
     queries with ``q_stride`` elements between rows.  bfloat16 steps in which every sequence
     brings one token run the split-context kernel, whose launch does not depend on the
     sequences' lengths; everything else runs the generic kernel."""
-    if q.dtype == torch.bfloat16 and batch.is_decode and head_dim % 8 == 0 and head_dim <= 256:
+    if batch.is_decode and attention_steps_from_device(q.dtype, head_dim):
         attention_decode(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table, batch.row_slot,
                          batch.row_pos, out, nq, nkv, head_dim, cache_view.page_size, window,
                          cache_view.page_table.shape[1] * cache_view.page_size, scale)
         return
+    require(not torch.cuda.is_current_stream_capturing(),
+            "attention: this dtype and head size run a kernel whose launch is sized from the host's lists of lengths, "
+            "which a captured step would freeze; such a model steps without CUDA graphs")
     if (q.dtype == torch.bfloat16 and q_stride % 8 == 0 and out.shape[1] % 8 == 0 and batch.max_new >= 48
             and lib().citlali_attention_prefill_tc_supports(_i(head_dim), _i(cache_view.page_size))):
         attention_prefill_tc(q, q_stride, cache_view.keys, cache_view.values, cache_view.page_table, batch.seq_start,

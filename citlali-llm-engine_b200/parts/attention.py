@@ -27,8 +27,6 @@ from .linear import DenseLinear
 
 
 class GQAttention:
-    graph_safe = True      # reads slots and positions from device memory only
-
     def __init__(self, params, prefix: str):
         self.hidden = int(params["hidden_size"])
         self.nq = int(params["num_heads"])
@@ -52,6 +50,13 @@ class GQAttention:
         self.qkv = DenseLinear(names, outs, self.hidden)
         self.o = DenseLinear([f"{prefix}.o_proj.weight"], [self.hidden], self.nq * self.d)
         self.q_gain = self.k_gain = None
+
+    @property
+    def graph_safe(self) -> bool:
+        """A step of single tokens reads slots and positions from device memory only: true once bound
+        to a dtype and head size that the split-context kernel takes; the other attention kernels size
+        their launch from the host's lists."""
+        return getattr(self, "dtype", None) is not None and ops.attention_steps_from_device(self.dtype, self.d)
 
     # ---- what it needs ---------------------------------------------------------------
     def tensor_specs(self):

@@ -60,11 +60,12 @@ class DenseLinear:
         self.dtype = ctx.dtype
         self.error_flag = ctx.error_flag
 
-    def bind_shared(self, weight: torch.Tensor, dtype):
+    def bind_shared(self, weight: torch.Tensor, ctx):
         """Use a matrix another part already holds (a head tied to the embedding)."""
         require(tuple(weight.shape) == (self.out_features, self.in_features), "shared matrix has the wrong shape")
         self.weight = weight
-        self.dtype = dtype
+        self.dtype = ctx.dtype
+        self.error_flag = ctx.error_flag
 
     def uses_tensor_cores(self, x: torch.Tensor) -> bool:
         return (self.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.in_features % 8 == 0

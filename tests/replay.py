@@ -66,6 +66,54 @@ def batched(requests, prompt_lens, batch_size):
     return steps
 
 
+def chunked(requests, batch_size, seed, low=2, high=40):
+    """Batches of `batch_size` requests that start together and then go on together by several tokens a
+    step: each live request brings its next `low`..`high` tokens (drawn per request and step), so that the
+    sequences of a step have unequal pasts and unequal numbers of new tokens.  Logits everywhere."""
+    import random
+    rng = random.Random(seed)
+    steps = []
+    for first in range(0, len(requests), batch_size):
+        pos = {rid: 0 for rid, _ in requests[first:first + batch_size]}
+        live = list(requests[first:first + batch_size])
+        while live:
+            entries, end, nxt = [], [], []
+            for rid, toks in live:
+                n = min(rng.randint(low, high), len(toks) - pos[rid])
+                entries.append({"id": rid, "tokens": toks[pos[rid]:pos[rid] + n], "want": list(range(n))})
+                pos[rid] += n
+                if pos[rid] == len(toks):
+                    end.append(rid)
+                else:
+                    nxt.append((rid, toks))
+            steps.append({"step": len(steps), "entries": entries, "end": end})
+            live = nxt
+    return steps
+
+
+def joining(requests, prompt_lens, every):
+    """One running batch that requests join while it runs: request i starts (its prompt in one step) at step
+    `i * every`, in the same step in which earlier requests go on by one token.  Logits at each prompt's end
+    and at every later token."""
+    steps, pos, live, waiting, t = [], {}, [], list(zip(requests, prompt_lens)), 0
+    while live or waiting:
+        entries, end, nxt = [], [], []
+        for rid, toks in live:
+            entries.append({"id": rid, "tokens": [toks[pos[rid]]], "want": [0]})
+            pos[rid] += 1
+            (end if pos[rid] == len(toks) else nxt).append(rid if pos[rid] == len(toks) else (rid, toks))
+        if waiting and t % every == 0:
+            (rid, toks), n = waiting.pop(0)
+            entries.append({"id": rid, "tokens": toks[:n], "want": [n - 1]})
+            pos[rid] = n
+            (end if n == len(toks) else nxt).append(rid if n == len(toks) else (rid, toks))
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": end})
+        live = nxt
+        t += 1
+    return steps
+
+
 def max_live_tokens(steps):
     """The most tokens live requests hold at any time, each rounded up to a multiple of 64."""
     held, best = {}, 0

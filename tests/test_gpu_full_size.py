@@ -3,12 +3,13 @@ of a second size of the family (hidden 5120, 40 / 8 heads, feed-forward 17408), 
 layers and random weights: the bfloat16 engine, whose kernels take their production shapes here (both forms of the
 tensor-core product with K splits over clusters, the product on pairs of SMs, the tcgen05 prompt attention, the cluster decode attention, the wide
 argmax), against the 32-bit engine on the same weight values; and the 32-bit engine against itself under another
-way of cutting the tokens.  No plain-implementation run at this size: the 32-bit engine is checked against it on
-the tiny configurations."""
+way of cutting the tokens.  The plain implementation runs at these layer sizes too, with a vocabulary of 8,192
+(its float64 copy of the real one would take 10 GB): both engines against it on a model folder."""
 import pytest
 import torch
 
 import citlali_b200 as cb
+import plain_qwen3 as plain
 from citlali_b200 import ops
 from helpers import random_tokens
 
@@ -119,3 +120,80 @@ def test_generation_at_production_shapes_repeats_bit_for_bit(sessions):
     a = [r.tokens for r in s16.generate(prompts, opts)]
     b = [r.tokens for r in s16.generate(prompts, opts)]
     assert a == b and all(len(t) == 96 for t in a)
+
+
+@pytest.mark.parametrize("batch", [8, 64])
+def test_replayed_decode_at_batch_8_and_64_equals_plain_steps(batch):
+    """The captured decode step at the batch sizes the benchmark runs (at 64 the swapped product takes its widest
+    tile and decode attention one block per sequence and head group) against ``session.step`` issued one by one:
+    the same logits bit for bit and the same tokens, for unequal prompts, over several steps."""
+    cfg = cb.config_from_dict(dict(SHAPE))
+    s = cb.InferenceSession().load_random(cfg, seed=7, max_context=512, dtype="bfloat16", max_batch=batch, gain_spread=0.1)
+    assert s.runner is not None
+    vocab = SHAPE["vocab_size"]
+    prompts = [random_tokens(vocab, 1 + (37 * i) % 150, 500 + i) for i in range(batch)]
+
+    def run(with_graph):
+        slots = [s.acquire() for _ in prompts]
+        logits = s.step([cb.StepEntry(sl, p, [len(p) - 1]) for sl, p in zip(slots, prompts)])
+        toks = s.sampler.sample(logits, 0.0, [])
+        seen_tokens, seen_logits = [list(toks)], []
+        for _ in range(5):
+            if with_graph:
+                s.runner.launch(slots, toks, 0.0, [])
+                toks = s.runner.read_tokens(batch)
+                seen_logits.append(s.runner.logits[(batch, True)].clone())
+            else:
+                logits = s.step([cb.StepEntry(sl, [t], [0]) for sl, t in zip(slots, toks)])
+                toks = s.sampler.sample(logits, 0.0, [])
+                seen_logits.append(logits.clone())
+            seen_tokens.append(list(toks))
+        for sl in slots:
+            s.release(sl)
+        s.check_device_errors()
+        return seen_tokens, seen_logits
+
+    graph_tokens, graph_logits = run(True)
+    plain_tokens, plain_logits = run(False)
+    assert graph_tokens == plain_tokens
+    for a, b in zip(graph_logits, plain_logits):
+        assert torch.equal(a, b)
+
+
+def test_production_layer_sizes_against_the_plain_implementation(tmp_path):
+    """Two layers of the benchmark's sizes (hidden 4096, 32 / 8 heads of 128, feed-forward 12288) written as a model
+    folder with a vocabulary of 8,192, loaded by both engines and by the plain implementation (float64): prompts of
+    unequal lengths in one step of 647 rows, then tokens one by one."""
+    shape = dict(SHAPE, vocab_size=8192)
+    cfg = cb.config_from_dict(shape)
+    folder = str(tmp_path / "model")
+    cb.write_random_model(folder, cfg, 77, dtype="bfloat16")
+    pcfg, w = plain.load_folder(folder)
+    lengths, decoded = [300, 17, 130, 200], 4
+    toks = [random_tokens(8192, n + decoded, 900 + n) for n in lengths]
+    want = [plain.model_logits(pcfg, w, t) for t in toks]
+    del w
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 2.5e-2)):
+        s = cb.InferenceSession().load_model(folder, max_context=512, dtype=dtype, max_batch=4)
+        slots = [s.acquire() for _ in toks]
+        tail = 8
+        out = s.step([cb.StepEntry(sl, t[:n], list(range(max(0, n - tail), n))) for sl, t, n in zip(slots, toks, lengths)])
+        out = out.double().cpu()
+        got, r = [], 0
+        for b, n in enumerate(lengths):
+            for p in range(max(0, n - tail), n):
+                got.append((b, p, out[r])); r += 1
+        for j in range(decoded):
+            out = s.step([cb.StepEntry(sl, [t[n + j]], [0]) for sl, t, n in zip(slots, toks, lengths)]).double().cpu()
+            for b, n in enumerate(lengths):
+                got.append((b, n + j, out[b]))
+        s.check_device_errors()
+        worst = 0.0
+        for b, p, row in got:
+            scale = float(want[b][p].abs().max())
+            err = float((row - want[b][p]).abs().max())
+            worst = max(worst, err / scale)
+            assert err <= tol * scale + 1e-6, f"{dtype} sequence {b} position {p}: |diff| {err:.3e} of {scale:.3e}"
+        print(f"[production layer sizes, {dtype}] worst |diff| / max|logit| = {worst:.3e} (limit {tol:.1e})")
+        del s
+        torch.cuda.empty_cache()

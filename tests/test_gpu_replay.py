@@ -84,6 +84,35 @@ def test_whole_tail_and_batched_agree_with_plain(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_sequences_that_go_on_by_several_tokens_and_requests_that_join(model_dirs, name, dtype):
+    """Steps whose sequences have unequal pasts AND bring unequal runs of 2 to 40 new tokens, three slots over
+    two batches; and one running batch that requests join while the others decode.  Both against the plain
+    implementation, and in 32-bit bitwise equal to each request run whole."""
+    stored = "float32" if dtype == "float32" else "bfloat16"
+    want = plain_rows(model_dirs, name, stored)
+    reqs = requests_for(name)[:6]
+    s = session_for(model_dirs, name, dtype, max_batch=3)
+    whole = replay.run_in_process(s, replay.whole(reqs))
+    steps = replay.chunked(reqs, 3, seed=5)
+    assert any(len(st["entries"]) >= 2 and len({len(e["tokens"]) for e in st["entries"]}) >= 2 for st in steps[1:])
+    cut = replay.run_in_process(s, steps)
+    assert set(cut) == set(whole)
+    check(cut, want, dtype, f"{name} {dtype} chunked")
+    reqs3 = reqs[:3]
+    lens = [max(1, len(t) - 20) for _, t in reqs3]
+    joined = replay.run_in_process(s, replay.joining(reqs3, lens, every=4))
+    check(joined, want, dtype, f"{name} {dtype} joining")
+    assert s.cache.slots.free_count == 3 and s.cache.pages_held() == 0
+    for got in (cut, joined):
+        for key, row in got.items():
+            if dtype == "float32":
+                assert torch.equal(row, whole[key]), f"{name}: logits at {key} depend on the cut"
+            else:
+                assert (row - whole[key]).abs().max() <= TOL[dtype] * whole[key].abs().max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(model_dirs, dtype):
     """A 3-token prompt, then 250 tokens one by one (across four cache pages); and the first
     tokens of sequences: prompts of one token, logits at position 0."""
@@ -101,7 +130,10 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
     check(got, want, dtype, f"C {dtype} first tokens")
     got1 = replay.run_in_process(s, replay.whole(firsts))
     for k in got:
-        assert torch.equal(got[k], got1[k]) if dtype == "float32" else True
+        if dtype == "float32":
+            assert torch.equal(got[k], got1[k])
+        else:       # a step of single tokens and a step of prompts run different kernels: rounding only
+            assert (got[k] - got1[k]).abs().max() <= TOL[dtype] * got1[k].abs().max()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -159,8 +191,6 @@ def test_step_refuses_what_it_cannot_run(model_dirs):
         s.step([cb.StepEntry(a, [1, 2], [3])])
     s.step([cb.StepEntry(a, [1, 2], [])])
     b = s.acquire()
-    with pytest.raises(cb.CitlaliError, match="no request joins"):
-        s.step([cb.StepEntry(a, [3], [0]), cb.StepEntry(b, [3], [0])])
     with pytest.raises(cb.CitlaliError, match="twice in one step"):
         s.step([cb.StepEntry(a, [3], [0]), cb.StepEntry(a, [3], [0])])
     assert s.cache.length(a) == 2                              # refused steps changed nothing

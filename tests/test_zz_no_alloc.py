@@ -40,12 +40,12 @@ def _case(seed, lengths, nq, nkv, d, page=64):
     return q, kp, vp, table.to(DEV), slots, pos
 
 
-def _no_alloc(lib, q, kp, vp, table, slots, pos, out, nq, nkv, d, page, max_positions):
+def _no_alloc(lib, q, kp, vp, table, slots, pos, out, nq, nkv, d, page, max_positions, window=0):
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     i = ctypes.c_int
     return lib.citlali_attention_decode_no_alloc(
         p(q), i(q.shape[1]), p(kp), p(vp), p(table), i(table.shape[1]), p(slots), p(pos), p(out), i(out.shape[1]),
-        i(out.shape[0]), i(nq), i(nkv), i(d), i(page), i(0), i(max_positions), ctypes.c_float(1.0 / math.sqrt(d)),
+        i(out.shape[0]), i(nq), i(nkv), i(d), i(page), i(window), i(max_positions), ctypes.c_float(1.0 / math.sqrt(d)),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
@@ -55,19 +55,49 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
     nq, nkv, d = 8, 2, 64
     # pages of 16 keys take the kernel pair that keeps per-chunk partials in the scratch array; pages of 64 take the
     # cluster kernel, which leaves the array alone.  Within each pair the second call sees what the first one left.
-    for seed, lengths, page in ((1, [700, 3, 257, 64], 16), (2, [5, 130, 1, 300], 16),
-                                (3, [700, 3, 257, 64], 64), (4, [5, 130, 1, 300], 64)):
+    # The last two calls attend to a window of keys only (chunks before the window are skipped).  Both entry
+    # points run the same kernels on the same inputs, so the results are equal bit for bit.
+    for seed, lengths, page, window in ((1, [700, 3, 257, 64], 16, 0), (2, [5, 130, 1, 300], 16, 0),
+                                        (3, [700, 3, 257, 64], 64, 0), (4, [5, 130, 1, 300], 64, 0),
+                                        (5, [700, 3, 257, 64], 16, 100), (6, [5, 130, 1, 300], 64, 37)):
         q, kp, vp, table, slots, pos = _case(seed, lengths, nq, nkv, d, page)
         max_positions = table.shape[1] * page
         want = torch.empty(len(lengths), nq * d, dtype=torch.bfloat16, device=DEV)
-        ops.attention_decode(q, q.shape[1], kp, vp, table, slots, pos, want, nq, nkv, d, page, 0, max_positions,
+        ops.attention_decode(q, q.shape[1], kp, vp, table, slots, pos, want, nq, nkv, d, page, window, max_positions,
                              1.0 / math.sqrt(d))
         got = torch.full_like(want, float("nan"))
-        rc = _no_alloc(lib, q, kp, vp, table, slots, pos, got, nq, nkv, d, page, max_positions)
+        rc = _no_alloc(lib, q, kp, vp, table, slots, pos, got, nq, nkv, d, page, max_positions, window)
         assert rc == 0, lib.citlali_last_error().decode()
         torch.cuda.synchronize()
-        err = float((got.float() - want.float()).abs().max())
-        assert err <= 2 ** -8 * float(want.float().abs().max()), f"call with seed {seed}: |diff| {err:.3e}"
+        assert torch.equal(got, want), f"call with seed {seed}: the two entry points differ"
+
+
+def test_no_alloc_entry_point_at_the_edge_of_its_array():
+    """The largest call the array holds is accepted and right; one chunk more is refused.  (A call's need is
+    a multiple of head size + 2, which divides no power of two for a legal head size: no call needs exactly
+    the array's 2^20 floats.  2 rows x 13 heads x 611 chunks x 66 is 100 floats short of it.)"""
+    lib = ops.lib()
+    lib.citlali_attention_decode_scratch_floats.restype = ctypes.c_size_t
+    nq, nkv, d, page = 13, 13, 64, 16
+    chunks = 611
+    max_positions = chunks * 2 * page
+    i = ctypes.c_int
+    assert lib.citlali_attention_decode_scratch_floats(i(2), i(nq), i(d), i(page), i(max_positions)) == (1 << 20) - 100
+    assert lib.citlali_attention_decode_scratch_floats(i(2), i(nq), i(d), i(page), i(max_positions + 1)) > (1 << 20)
+    q, kp, vp, table, slots, pos = _case(7, [max_positions, 301], nq, nkv, d, page)
+    want = torch.empty(2, nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(q, q.shape[1], kp, vp, table, slots, pos, want, nq, nkv, d, page, 0, max_positions,
+                         1.0 / math.sqrt(d))
+    got = torch.full_like(want, float("nan"))
+    rc = _no_alloc(lib, q, kp, vp, table, slots, pos, got, nq, nkv, d, page, max_positions)
+    assert rc == 0, lib.citlali_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    out = torch.zeros_like(want)
+    rc = _no_alloc(lib, q, kp, vp, table, slots, pos, out, nq, nkv, d, page, max_positions + 1)
+    assert rc < 0 and "built-in array holds 1048576" in lib.citlali_last_error().decode()
+    torch.cuda.synchronize()
+    assert float(out.float().abs().sum()) == 0.0
 
 
 def test_no_alloc_entry_point_refuses_what_exceeds_its_array():
