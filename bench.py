@@ -99,7 +99,7 @@ def run_workload(index, repetitions):
     import citlali_b200 as cb
 
     w = workload_from_baseline(index)
-    context = -(-(w["longest"] + w["decode_steps"]) // 64) * 64
+    context = -(-(w["longest"] + w["decode_steps"]) // cb.PAGE_SIZE) * cb.PAGE_SIZE
     cfg = cb.config_from_dict(dict(
         architectures=["Qwen3ForCausalLM"], num_hidden_layers=w["num_hidden_layers"], hidden_size=w["hidden_size"],
         num_attention_heads=w["num_attention_heads"], num_key_value_heads=w["num_key_value_heads"], head_dim=w["head_dim"],

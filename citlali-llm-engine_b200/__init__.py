@@ -10,8 +10,8 @@ from .config import (QwenConfig, ModelSpec, LayerSpec, PartSpec, ScheduleStep, c
                      unregister_architecture)
 from .weights import (SafetensorsFile, TensorSpec, WeightHandle, WeightLoader, write_random_model,
                       write_safetensors)
-from .cache import KVRequirement, SequenceCache, StateRequirement
-from .parts import BuildContext, StepBatch, register_part, registered_parts, unregister_part
+from .cache import PAGE_SIZE, KVRequirement, SequenceCache, StateRequirement
+from .parts import BuildContext, StepBatch, build_part, register_part, registered_parts, unregister_part
 from .engine import (DecoderModel, GenerationOptions, GenerationResult, InferenceSession, StepEntry,
                      StopReason, expected_tensors, run_generation)
 from .sampling import Sampler, uniform

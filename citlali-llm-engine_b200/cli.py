@@ -148,10 +148,25 @@ def print_model_info(model_path: str, out=sys.stdout) -> None:
     print(f"tensors: {len(tensors)}", file=out)
     print(f"parameters: {params}", file=out)
     print(f"bfloat16 weight bytes: {2 * params}", file=out)
-    kv = sum(2 * l.mixer.params["num_kv_heads"] * l.mixer.params["head_dim"]
-             for l in (spec.layers[s.layer] for s in spec.schedule if s.cache_of is None)
-             if "num_kv_heads" in l.mixer.params)
+    from .cache import KVRequirement, StateRequirement
+    from .engine.model import cache_requirements_of
+    kv = state = 0
+    for req in cache_requirements_of(spec):
+        if isinstance(req, KVRequirement):
+            kv += 2 * req.num_kv_heads * req.head_dim
+        elif isinstance(req, StateRequirement):
+            n = torch_element_size(req.dtype)
+            for s in req.shape:
+                n *= s
+            state += n
     print(f"cache bytes per token (bfloat16): {2 * kv}", file=out)
+    if state:
+        print(f"state bytes per sequence: {state}", file=out)
+
+
+def torch_element_size(dtype) -> int:
+    import torch
+    return torch.tensor([], dtype=dtype).element_size()
 
 
 def run_cli(argv: List[str]) -> int:

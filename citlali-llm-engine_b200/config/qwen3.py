@@ -37,6 +37,21 @@ def _positive_float(d, key):
     return float(v)
 
 
+def _rope_theta(d) -> float:
+    """``rope_theta``, or the same number inside a ``rope_parameters`` object (how newer writers of
+    config.json store it); a ``rope_type`` other than the plain one there is a scaling, which is refused."""
+    params = d.get("rope_parameters")
+    if params is not None:
+        require(isinstance(params, dict), "config.json: 'rope_parameters' must be an object")
+        kind = params.get("rope_type", params.get("type", "default"))
+        require(kind in (None, "default"),
+                f"config.json: rope_parameters.rope_type '{kind}' is not supported (plain rotary positions only)")
+        if "rope_theta" not in d:
+            require("rope_theta" in params, "config.json: required key 'rope_theta' is missing (also from 'rope_parameters')")
+            return _positive_float(params, "rope_theta")
+    return _positive_float(d, "rope_theta")
+
+
 @dataclass(frozen=True)
 class QwenConfig:
     architecture: str
@@ -109,7 +124,7 @@ class QwenConfig:
             num_key_value_heads=kv_heads,
             head_dim=head_dim,
             rms_norm_eps=_positive_float(d, "rms_norm_eps"),
-            rope_theta=_positive_float(d, "rope_theta"),
+            rope_theta=_rope_theta(d),
             tie_word_embeddings=tie,
             eos_token_ids=eos_ids,
         )
@@ -154,9 +169,9 @@ class QwenConfig:
         for i in range(self.num_hidden_layers):
             base = f"model.layers.{i}"
             norm = {"size": self.hidden_size, "eps": self.rms_norm_eps}
-            layers.append(LayerSpec(
-                block="pre_norm_residual",
-                mixer=PartSpec("gqa_attention", {
+            layers.append(LayerSpec(block="pre_norm_residual", parts={
+                "mixer_norm": PartSpec("rms_norm", dict(norm), f"{base}.input_layernorm"),
+                "mixer": PartSpec("gqa_attention", {
                     "hidden_size": self.hidden_size,
                     "num_heads": self.num_attention_heads,
                     "num_kv_heads": self.num_key_value_heads,
@@ -166,13 +181,12 @@ class QwenConfig:
                                  "rotary_dim": self.head_dim},
                     "window": None,
                 }, f"{base}.self_attn"),
-                feed_forward=PartSpec("gated_silu", {
+                "feed_forward_norm": PartSpec("rms_norm", dict(norm), f"{base}.post_attention_layernorm"),
+                "feed_forward": PartSpec("gated_silu", {
                     "hidden_size": self.hidden_size,
                     "intermediate_size": self.intermediate_size,
                 }, f"{base}.mlp"),
-                mixer_norm=PartSpec("rms_norm", dict(norm), f"{base}.input_layernorm"),
-                feed_forward_norm=PartSpec("rms_norm", dict(norm), f"{base}.post_attention_layernorm"),
-            ))
+            }))
         spec = ModelSpec(
             architecture=self.architecture,
             vocab_size=self.vocab_size,

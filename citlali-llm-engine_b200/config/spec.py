@@ -9,7 +9,7 @@ architecture's config directly.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, Optional, Tuple
+from typing import Any, Dict, Mapping, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -23,14 +23,20 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer with weights of its own: an arrangement (``block``) of a mixer, a
-    feed-forward and their norms."""
+    """One layer with weights of its own: an arrangement (``block``) and the parts it arranges, by name,
+    in the order given.  Which names a block kind needs, and which registry each is looked up in, is the
+    block's business: the pre-norm block takes ``mixer_norm``, ``mixer``, ``feed_forward_norm`` and
+    ``feed_forward`` (either pair may be absent); a block with four norms, or with one norm shared by a
+    mixer and a feed-forward that run side by side, names its parts as it likes."""
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, PartSpec]
     block_params: Dict[str, Any] = field(default_factory=dict)
+
+    def part(self, name: str) -> PartSpec:
+        from ..errors import require
+        require(name in self.parts, f"a '{self.block}' layer needs a part named '{name}'; it has: "
+                                    f"{', '.join(self.parts) or '(none)'}")
+        return self.parts[name]
 
 
 @dataclass(frozen=True)
@@ -55,6 +61,8 @@ class ModelSpec:
     head_name: str
     tie_head_to_embedding: Optional[bool]   # None: tied iff the head tensor is absent
     stop_token_ids: Tuple[int, ...] = ()
+    embedding_scale: Optional[float] = None  # the embedding rows are multiplied by it (None: a plain row copy)
+    logit_scale: Optional[float] = None      # the logits are multiplied by it (None: as the output matrix gives them)
 
     def validate(self):
         from ..errors import require

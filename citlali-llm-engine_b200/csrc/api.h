@@ -15,9 +15,12 @@ const char* citlali_last_error(void);
 // finished, and wait for it on the device; 0: plain stream order.
 void citlali_set_dependent_launch(int enabled);
 
-// out[m, :] = table[tokens[m], :] widened to float32.
+// out[m, :] = table[tokens[m], :] widened to float32 and multiplied by `scale` (1: a plain row copy).
 int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
-                       int rows, int hidden, int vocab, int32_t* error_flag, cudaStream_t stream);
+                       int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream);
+
+// x[0..n) *= scale.
+int citlali_scale(float* x, size_t n, float scale, cudaStream_t stream);
 
 // out[r, :] = x[idx[r], :] * rsqrt(mean(x^2) + eps) * gain   (idx may be null: identity).
 int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,
@@ -35,7 +38,9 @@ int citlali_gemm_simt(const void* x, int x_dtype, const void* w, int w_dtype, vo
 
 // In place on a [rows, (nq + 2 nkv) d] projection: per-head RMSNorm of q and k, half-split
 // rotation by the row's position, then k and v written to the paged cache of the row's slot.
-// write_cache == 0 leaves the cache alone (a layer that reads another layer's cache).
+// The first `rotary_dim` elements of a head are rotated in pairs (i, i + rotary_dim/2), the rest pass through.
+// write_cache: 0 leaves the cache alone (a layer that reads another layer's cache); 1 stores k and v; 2 writes
+// the normed, rotated k back into the row instead and leaves v alone (a second call then stores them).
 int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_gain, const void* k_gain, int gain_dtype,
                                const float* inv_freq, int rotary_dim,
                                const int32_t* row_slot, const int32_t* row_pos,

@@ -18,17 +18,22 @@ constexpr int kMaxPairsPerLane = 4;   // head_dim <= 256: 128 rotation pairs ove
 //   k, v: stored at the row's position in the slot's pages (store_kv_kernel,
 //         kernels.cu:524-533), k after norm and rotation, v as projected.
 constexpr int kRopeWarps = 8;      // warps per block
-constexpr int kRopeBatch = 1;      // heads a warp has in flight (more than one was measured slower)
+constexpr int kMaxTailPerLane = 8; // head elements past the rotated ones: at most 254 over 32 lanes
 
-template <typename T, typename TG>
+// `write_cache`: 0 nothing is stored to the cache (a layer that reads another layer's keys); 1 keys and
+// values go to the cache; 2 the normed (and rotated) keys go back into the row instead and values stay
+// where they are, for a position encoding that works on the row between this kernel and the cache write.
+// PARTIAL: only the first `rotary_dim` elements of a head are rotated, in pairs (i, i + rotary_dim/2);
+// the rest are normed and pass through.
+template <typename T, typename TG, bool PARTIAL>
 __global__ void __launch_bounds__(kRopeWarps * 32)
 qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
-                          const float* __restrict__ inv_freq,
+                          const float* __restrict__ inv_freq, int rotary_dim,
                           const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                           const int32_t* __restrict__ page_table, int page_table_stride,
                           T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
                           int nq, int nkv, int d, float eps, int write_cache, int heads_per_block) {
-    extern __shared__ float2 cos_sin[];                 // [d / 2]: the row's rotation, shared by the block's heads
+    extern __shared__ float2 cos_sin[];                 // [rotary_dim / 2]: the row's rotation, shared by the block's heads
     dependents_may_launch();
     // positions, slots and page tables come from the host before the step: the rotation and the row's place in
     // the cache are worked out while the kernel ahead (the projection) is still running
@@ -38,14 +43,15 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
     const int head_begin = blockIdx.y * heads_per_block;
     const int head_end = min(total, head_begin + heads_per_block);
     const int half = d >> 1;
+    const int rh = PARTIAL ? (rotary_dim >> 1) : half;  // pairs that are rotated, and the distance within a pair
     const int pos = row_pos[row];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    for (int i = threadIdx.x; i < rh; i += blockDim.x) {
         float sn, cs;
         sincosf((float)pos * inv_freq[i], &sn, &cs);
         cos_sin[i] = make_float2(cs, sn);
     }
     size_t page_off = 0;
-    if (write_cache) {
+    if (write_cache == 1) {
         const int page = page_table[(size_t)row_slot[row] * page_table_stride + pos / page_size];
         page_off = ((size_t)page * nkv * page_size + (pos % page_size)) * d;       // + kv head * page_size * d
     }
@@ -53,60 +59,73 @@ qk_norm_rope_cache_kernel(T* __restrict__ qkv, const TG* __restrict__ q_gain, co
     wait_for_predecessor();
     T* row_ptr = qkv + (size_t)row * total * d;
 
-    // a warp takes heads warp, warp + 8, ...; it loads kRopeBatch of them before it works on any
-    for (int h0 = head_begin + warp; h0 < head_end; h0 += kRopeWarps * kRopeBatch) {
-        float x0[kRopeBatch][kMaxPairsPerLane], x1[kRopeBatch][kMaxPairsPerLane];
+    // a warp takes heads warp, warp + 8, ...
+    for (int head = head_begin + warp; head < head_end; head += kRopeWarps) {
+        const bool is_v = head >= nq + nkv;
+        // a value head is copied as two halves; a query or key head as its pairs and, if PARTIAL, its tail
+        const int step = is_v ? half : rh;
+        float x0[kMaxPairsPerLane], x1[kMaxPairsPerLane], tail[PARTIAL ? kMaxTailPerLane : 1];
 #pragma unroll
-        for (int b = 0; b < kRopeBatch; ++b) {
-            const int head = h0 + b * kRopeWarps;
+        for (int j = 0; j < kMaxPairsPerLane; ++j) {
+            const int i = lane + 32 * j;
+            const bool on = i < step;
+            x0[j] = on ? ldf(row_ptr, (size_t)head * d + i) : 0.0f;
+            x1[j] = on ? ldf(row_ptr, (size_t)head * d + i + step) : 0.0f;
+        }
+        if (PARTIAL) {
 #pragma unroll
-            for (int j = 0; j < kMaxPairsPerLane; ++j) {
-                const int i = lane + 32 * j;
-                const bool on = head < head_end && i < half;
-                x0[b][j] = on ? ldf(row_ptr, (size_t)head * d + i) : 0.0f;
-                x1[b][j] = on ? ldf(row_ptr, (size_t)head * d + i + half) : 0.0f;
+            for (int j = 0; j < kMaxTailPerLane; ++j) {
+                const int i = 2 * rh + lane + 32 * j;
+                tail[j] = (!is_v && i < d) ? ldf(row_ptr, (size_t)head * d + i) : 0.0f;
             }
         }
+        if (is_v) {                                     // a value head goes to the cache as it is
+            if (write_cache == 1) {
+                T* dst = v_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
 #pragma unroll
-        for (int b = 0; b < kRopeBatch; ++b) {
-            const int head = h0 + b * kRopeWarps;
-            if (head >= head_end) break;
-            if (head >= nq + nkv) {                     // a value head goes to the cache as it is
-                if (write_cache) {
-                    T* dst = v_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
-#pragma unroll
-                    for (int j = 0; j < kMaxPairsPerLane; ++j) {
-                        const int i = lane + 32 * j;
-                        if (i < half) { stf(dst, i, x0[b][j]); stf(dst, i + half, x1[b][j]); }
-                    }
+                for (int j = 0; j < kMaxPairsPerLane; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < half) { stf(dst, i, x0[j]); stf(dst, i + half, x1[j]); }
                 }
-                continue;
             }
-            const bool is_q = head < nq;
-            const TG* gain = is_q ? q_gain : k_gain;
-            float ss = 0.0f;
+            continue;
+        }
+        const bool is_q = head < nq;
+        const TG* gain = is_q ? q_gain : k_gain;
+        float ss = 0.0f;
 #pragma unroll
-            for (int j = 0; j < kMaxPairsPerLane; ++j) {
-                ss = fmaf(x0[b][j], x0[b][j], ss);
-                ss = fmaf(x1[b][j], x1[b][j], ss);
-            }
-            ss = warp_sum(ss);
-            const float inv = gain ? rsqrtf(ss / (float)d + eps) : 1.0f;
-            if (!is_q && !write_cache) continue;
-            T* dst = is_q ? row_ptr + (size_t)head * d : k_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+        for (int j = 0; j < kMaxPairsPerLane; ++j) {
+            ss = fmaf(x0[j], x0[j], ss);
+            ss = fmaf(x1[j], x1[j], ss);
+        }
+        if (PARTIAL) {
 #pragma unroll
-            for (int j = 0; j < kMaxPairsPerLane; ++j) {
-                const int i = lane + 32 * j;
-                if (i < half) {
-                    float a = x0[b][j], c2 = x1[b][j];
-                    if (gain) {
-                        a = a * inv * ldf(gain, i);
-                        c2 = c2 * inv * ldf(gain, i + half);
-                    }
-                    const float c = cos_sin[i].x, sn = cos_sin[i].y;
-                    stf(dst, i, a * c - c2 * sn);
-                    stf(dst, i + half, a * sn + c2 * c);
+            for (int j = 0; j < kMaxTailPerLane; ++j) ss = fmaf(tail[j], tail[j], ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = gain ? rsqrtf(ss / (float)d + eps) : 1.0f;
+        if (!is_q && write_cache == 0) continue;
+        T* dst = (is_q || write_cache == 2) ? row_ptr + (size_t)head * d
+                                            : k_pool + page_off + (size_t)((head - nq) % nkv) * page_size * d;
+#pragma unroll
+        for (int j = 0; j < kMaxPairsPerLane; ++j) {
+            const int i = lane + 32 * j;
+            if (i < rh) {
+                float a = x0[j], c2 = x1[j];
+                if (gain) {
+                    a = a * inv * ldf(gain, i);
+                    c2 = c2 * inv * ldf(gain, i + rh);
                 }
+                const float c = cos_sin[i].x, sn = cos_sin[i].y;
+                stf(dst, i, a * c - c2 * sn);
+                stf(dst, i + rh, a * sn + c2 * c);
+            }
+        }
+        if (PARTIAL) {
+#pragma unroll
+            for (int j = 0; j < kMaxTailPerLane; ++j) {
+                const int i = 2 * rh + lane + 32 * j;
+                if (i < d) stf(dst, i, gain ? tail[j] * inv * ldf(gain, i) : tail[j]);
             }
         }
     }
@@ -291,11 +310,17 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
         set_last_error("qk_norm_rope_cache: head size %d must be even and at most %d", head_dim, 64 * kMaxPairsPerLane);
         return kBadShape;
     }
-    if (rotary_dim != head_dim) {
-        set_last_error("qk_norm_rope_cache: rotating %d of %d head elements is not implemented (whole head only)",
+    if (rotary_dim <= 0 || rotary_dim % 2 != 0 || rotary_dim > head_dim) {
+        set_last_error("qk_norm_rope_cache: the rotated part of a head (%d elements) must be even and at most the head size %d",
                        rotary_dim, head_dim);
         return kBadShape;
     }
+    if (write_cache < 0 || write_cache > 2) {
+        set_last_error("qk_norm_rope_cache: write_cache must be 0 (nothing), 1 (to the cache) or 2 (keys back into the row), not %d",
+                       write_cache);
+        return kBadShape;
+    }
+    const bool partial = rotary_dim != head_dim;
     if (cache_dtype != dtype) {
         set_last_error("qk_norm_rope_cache: the cache's dtype must equal the activations'");
         return kBadDType;
@@ -315,7 +340,7 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
     }
     // bfloat16 with a power-of-two number of 16-byte pieces in half a head: the kernel that moves 16-byte words
     const int lanes = head_dim / 16;
-    if (dtype == kBF16 && head_dim % 16 == 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 &&
+    if (!partial && write_cache != 2 && dtype == kBF16 && head_dim % 16 == 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 &&
         ((uintptr_t)qkv & 15u) == 0 && ((uintptr_t)k_pool & 15u) == 0 && ((uintptr_t)v_pool & 15u) == 0) {
         const int per_pass = kRopeVecThreads / lanes;
         const int vec_heads = rows >= 128 ? total : per_pass;
@@ -330,9 +355,15 @@ extern "C" int citlali_qk_norm_rope_cache(void* qkv, int dtype, const void* q_ga
     }
     return CITLALI_DISPATCH_FLOAT(dtype, T, [&] {
         return CITLALI_DISPATCH_FLOAT(gain_dtype, TG, [&] {
-            launch_kernel(qk_norm_rope_cache_kernel<T, TG>, grid, kRopeWarps * 32, (size_t)(head_dim / 2) * sizeof(float2), stream, 
-                (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, row_slot, row_pos, page_table,
-                page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache, heads_per_block);
+            if (partial) {
+                launch_kernel(qk_norm_rope_cache_kernel<T, TG, true>, grid, kRopeWarps * 32, (size_t)(rotary_dim / 2) * sizeof(float2), stream,
+                    (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, rotary_dim, row_slot, row_pos, page_table,
+                    page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache, heads_per_block);
+            } else {
+                launch_kernel(qk_norm_rope_cache_kernel<T, TG, false>, grid, kRopeWarps * 32, (size_t)(head_dim / 2) * sizeof(float2), stream,
+                    (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, inv_freq, rotary_dim, row_slot, row_pos, page_table,
+                    page_table_stride, (T*)k_pool, (T*)v_pool, page_size, nq, nkv, head_dim, eps, write_cache, heads_per_block);
+            }
             return CITLALI_LAUNCH_CHECK();
         });
     });

@@ -39,6 +39,19 @@ __device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepco
 
 bool dependent_launch_enabled();
 
+// The number of SMs of the current device, asked once per device.
+inline int device_sm_count() {
+    static int cached[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (cached[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 1;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};

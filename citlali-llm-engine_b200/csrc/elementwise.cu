@@ -20,11 +20,12 @@ void set_last_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-// x = E[token], a row copy with no scaling (reference: embed_kernel, kernels.cu:27-35).
+// x = E[token] * scale; the reference copies the row with no scaling (embed_kernel, kernels.cu:27-35),
+// which is scale = 1 (a product with 1.0f changes no bit).
 // A token outside the vocabulary is not read: the row is zeroed and the flag is raised.
 template <typename TW>
 __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* __restrict__ tokens,
-                                  float* __restrict__ out, int hidden, int vocab, int32_t* error_flag) {
+                                  float* __restrict__ out, int hidden, int vocab, float scale, int32_t* error_flag) {
     dependents_may_launch();
     wait_for_predecessor();
     const int row = blockIdx.x;
@@ -33,7 +34,14 @@ __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* _
     if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
     const TW* src = table + (size_t)(ok ? tok : 0) * hidden;
     float* dst = out + (size_t)row * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ldf(src, i) : 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ldf(src, i) * scale : 0.0f;
+}
+
+// x *= scale over n floats (a logit scale; the reference has none).
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float scale) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
 }
 
 // inv = rsqrt(sum x^2 / n + eps); y = x * inv * gain (reference: rms_norm_kernel,
@@ -141,12 +149,19 @@ extern "C" const char* citlali_last_error(void) { return g_last_error; }
 extern "C" void citlali_set_dependent_launch(int enabled) { g_dependent_launch = enabled != 0; }
 
 extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
-                                  int rows, int hidden, int vocab, int32_t* error_flag, cudaStream_t stream) {
+                                  int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     return CITLALI_DISPATCH_FLOAT(table_dtype, TW, [&] {
-        launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, error_flag);
+        launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, scale, error_flag);
         return CITLALI_LAUNCH_CHECK();
     });
+}
+
+extern "C" int citlali_scale(float* x, size_t n, float scale, cudaStream_t stream) {
+    if (n == 0) return 0;
+    const size_t blocks = (n + 255) / 256;
+    launch_kernel(scale_kernel, (int)(blocks < 4096 ? blocks : 4096), 256, 0, stream, x, n, scale);
+    return CITLALI_LAUNCH_CHECK();
 }
 
 extern "C" int citlali_rms_norm(const float* x, const void* gain, int gain_dtype, const int32_t* row_index,

@@ -507,7 +507,7 @@ static bool runs_on_pairs(int M, int N, int K, const Plan& pl) {
 }
 
 extern "C" int citlali_gemm_tc_runs_on_pairs(int M, int N, int K, int sm_count, int gate_runs) {
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = device_sm_count();
     return runs_on_pairs(M, N, K, make_plan(M, N, K, sm_count, 0, gate_runs != 0)) ? 1 : 0;
 }
 
@@ -543,7 +543,7 @@ extern "C" int citlali_wait_selftest(int32_t* error_flag, int* result, long long
 
 // How the product of this shape would run: *swapped, *bn and the K split (*splits).
 extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, int* swapped, int* bn, int* splits) {
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = device_sm_count();
     Plan pl = make_plan(M, N, K, sm_count, force_splits);
     if (swapped) *swapped = pl.swapped;
     if (bn) *bn = pl.bn;
@@ -582,7 +582,7 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
         set_last_error("gemm_tc: the gate epilogue needs a bfloat16 output and N a multiple of 32 (N %d)", N);
         return kBadShape;
     }
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = device_sm_count();
     const Plan pl = make_plan(M, N, K, sm_count, force_splits, swiglu);
     if (runs_on_pairs(M, N, K, pl)) return citlali_gemm_tc_pair(x, w, y, y_dtype, M, N, K, mode, error_flag, stream);
     GemmParams p;

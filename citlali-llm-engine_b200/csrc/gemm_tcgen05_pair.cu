@@ -207,7 +207,7 @@ static int resident_pairs(size_t smem) {
         return 0;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * 148);
+    cfg.gridDim = dim3(2 * device_sm_count());
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];

@@ -29,6 +29,8 @@ from ..parts.base import StepBatch
 def model_is_graph_safe(model) -> bool:
     """Every part of every layer, as bound, steps from device memory alone."""
     for block in model.layers:
+        if getattr(block, "graph_safe", True) is False:        # an arrangement may veto for code of its own
+            return False
         for part in block.parts():
             if not getattr(part, "graph_safe", False):
                 return False

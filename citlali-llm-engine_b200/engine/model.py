@@ -15,9 +15,16 @@ import torch
 from .. import ops
 from ..config.spec import ModelSpec
 from ..errors import require
-from ..parts.base import BuildContext, StepBatch, part_class
+from ..parts.base import BuildContext, StepBatch, build_part, part_class
 from ..parts.linear import DenseLinear
 from ..weights.loader import TensorSpec, WeightHandle
+
+
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
 
 
 def _build_layers(spec: ModelSpec):
@@ -29,8 +36,7 @@ def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
     specs = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size), "matrix")]
     for block in _build_layers(spec):
         specs.extend(block.tensor_specs())
-    norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix)
-    specs.extend(norm.tensor_specs())
+    specs.extend(build_part("norm", spec.final_norm).tensor_specs())
     # tied: the head is the embedding and a stored head is ignored; undecided: used if present
     specs.append(TensorSpec(spec.head_name, (spec.vocab_size, spec.hidden_size), "matrix",
                             optional=spec.tie_head_to_embedding is not False))
@@ -41,13 +47,20 @@ def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
     return specs
 
 
+def cache_requirements_of(spec: ModelSpec, layers=None) -> List[object]:
+    """Per schedule step: what it keeps (a KVRequirement, a StateRequirement, or None for a step that keeps
+    nothing or reads another step's cache).  No device is touched."""
+    layers = layers if layers is not None else _build_layers(spec)
+    return [None if step.cache_of is not None else layers[step.layer].cache_requirement() for step in spec.schedule]
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, ctx: BuildContext):
         spec.validate()
         self.spec = spec
         self.ctx = ctx
         self.layers = _build_layers(spec)
-        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix)
+        self.final_norm = build_part("norm", spec.final_norm)
         self.head = DenseLinear([spec.head_name], [spec.vocab_size], spec.hidden_size)
         self.embedding: Optional[torch.Tensor] = None
         self.tied = None
@@ -56,20 +69,16 @@ class DecoderModel:
         return expected_tensors(self.spec)
 
     def cache_requirements(self) -> List[object]:
-        """Per schedule step: what it keeps (None for a step that keeps nothing or reads
-        another step's cache)."""
-        out = []
-        for step in self.spec.schedule:
-            out.append(None if step.cache_of is not None else self.layers[step.layer].cache_requirement())
-        return out
+        return cache_requirements_of(self.spec, self.layers)
 
     def bind(self, weights: Dict[str, WeightHandle]) -> None:
         ctx, spec = self.ctx, self.spec
-        emb = weights[spec.embedding_name].tensor
+        emb = weights[spec.embedding_name]
         require(tuple(emb.shape) == (spec.vocab_size, spec.hidden_size),
                 f"unexpected tensor shape for {spec.embedding_name}: got {list(emb.shape)}, "
                 f"expected {[spec.vocab_size, spec.hidden_size]}")
-        self.embedding = emb.to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.embedding = torch.empty((spec.vocab_size, spec.hidden_size), dtype=ctx.dtype, device=ctx.device)
+        emb.copy_into(self.embedding)
         for block in self.layers:
             block.bind(weights, ctx)
         self.final_norm.bind(weights, ctx)
@@ -84,22 +93,21 @@ class DecoderModel:
             self.head.bind(weights, ctx)
 
     def weight_bytes_read_per_step(self) -> int:
-        """Bytes of weights one step reads when each matrix it uses is read once (embedding rows
-        and norm gains are left out: they are thousands of times smaller)."""
-        total = self.head.nbytes
-        for step in self.spec.schedule:
-            block = self.layers[step.layer]
-            for part in block.parts():
-                for lin in vars(part).values():
-                    if isinstance(lin, DenseLinear):
-                        total += lin.nbytes
-        return total
+        """Bytes of weights one step reads when each matrix it uses is read once: every tensor the layers
+        declare as a matrix (``tensor_specs()``, so lists of matrices inside a part count too), once per
+        schedule step that runs the layer, plus the output matrix.  The embedding's rows and the norm
+        gains are left out: they are thousands of times smaller."""
+        size = torch.tensor([], dtype=self.ctx.dtype).element_size()
+        per_layer = [sum(_numel(t.shape) for t in block.tensor_specs() if t.role == "matrix") * size
+                     for block in self.layers]
+        return self.head.nbytes + sum(per_layer[step.layer] for step in self.spec.schedule)
 
     def forward(self, batch: StepBatch, cache) -> torch.Tensor:
         """Logits ``[wanted, vocab]`` float32 for ``batch.want_rows``, in that order."""
         ctx, spec = self.ctx, self.spec
         x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag)
+        ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag,
+                       1.0 if spec.embedding_scale is None else float(spec.embedding_scale))
         for i, step in enumerate(spec.schedule):
             source = i if step.cache_of is None else step.cache_of
             view = cache.view(source) if cache.has_view(source) else None
@@ -108,4 +116,7 @@ class DecoderModel:
         if wanted == 0:
             return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=ctx.device)
         h = self.final_norm.forward(x, row_index=batch.want_rows)
-        return self.head.forward(h, out_dtype=torch.float32)
+        logits = self.head.forward(h, out_dtype=torch.float32)
+        if spec.logit_scale is not None:
+            ops.scale_(logits, float(spec.logit_scale))
+        return logits

@@ -13,13 +13,13 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
-from ..cache import SequenceCache
+from ..cache import PAGE_SIZE, SequenceCache
 from ..config.registry import config_from_model_dir
 from ..errors import CitlaliError, require
 from ..parts.base import BuildContext
 from ..sampling.sampler import Sampler
 from ..weights.loader import WeightHandle, WeightLoader
-from ..weights.random_init import random_weights
+from ..weights.random_init import random_tensor
 from .graph import DecodeGraphRunner, model_is_graph_safe
 from .generate import GenerationOptions, GenerationResult, run_generation
 from .model import DecoderModel
@@ -53,6 +53,7 @@ class InferenceSession:
         self.stats: Dict[str, float] = {}
         self.runner = None
         self.use_graphs = True     # set False before loading to step without CUDA graphs
+        self.page_size = PAGE_SIZE  # tokens a cache page holds; set before loading (the tensor-core attention kernels take 64)
 
     # ---- loading ---------------------------------------------------------------------
     def load_model(self, model_path: str, max_context: int = 2048, dtype="bfloat16", device="cuda:0",
@@ -91,8 +92,10 @@ class InferenceSession:
         for s in model.tensor_specs():
             if s.optional and spec.tie_head_to_embedding is not False:
                 continue
-            t = random_weights([s], seed, stored, device=dev, gain_spread=gain_spread)[s.name]
-            handles[s.name] = WeightHandle(s.name, t.dtype, tuple(t.shape), t)
+            # made when a part asks, and not kept: the model's own buffers are the only copy that stays
+            make = (lambda s=s: random_tensor(s, seed, stored, dev, gain_spread=gain_spread))
+            handles[s.name] = WeightHandle(s.name, torch.int32 if s.role == "table" else stored, tuple(s.shape),
+                                           produce=make)
         model.bind(handles)
         return self._finish(config, model, max_context, max_batch, max_tokens)
 
@@ -106,7 +109,7 @@ class InferenceSession:
         self.model = model
         self.max_context = min(int(max_context), model.spec.max_positions)
         capacity = int(max_tokens) if max_tokens is not None else None
-        page = 64
+        page = int(self.page_size)
         if capacity is None:
             capacity = max_batch * ((self.max_context + page - 1) // page) * page
         self.cache = SequenceCache(model.cache_requirements(), max_batch, capacity, self.max_context,

@@ -77,13 +77,21 @@ _i = ctypes.c_int
 _f = ctypes.c_float
 
 
-def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor):
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor,
+               scale: float = 1.0):
     _need_cuda(table, tokens, out, error_flag)
     require(tokens.dtype == torch.int32 and out.dtype == torch.float32, "embed_rows: tokens int32, out float32")
     rows, hidden = out.shape
     require(table.shape[1] == hidden and tokens.numel() == rows, "embed_rows: shapes do not fit")
     _check(lib().citlali_embed_rows(_ptr(table), _i(_dtype_code(table)), _ptr(tokens), _ptr(out), _i(rows),
-                                    _i(hidden), _i(table.shape[0]), _ptr(error_flag), _stream()), "embed_rows")
+                                    _i(hidden), _i(table.shape[0]), _f(scale), _ptr(error_flag), _stream()), "embed_rows")
+
+
+def scale_(x: torch.Tensor, scale: float):
+    """x *= scale in place (float32)."""
+    _need_cuda(x)
+    require(x.dtype == torch.float32, "scale_: float32 only")
+    _check(lib().citlali_scale(_ptr(x), ctypes.c_size_t(x.numel()), _f(scale), _stream()), "scale")
 
 
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
@@ -120,6 +128,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: boo
 
 def qk_norm_rope_cache(qkv, q_gain, k_gain, inv_freq, rotary_dim, row_slot, row_pos, page_table,
                        k_pool, v_pool, page_size, nq, nkv, head_dim, eps, write_cache=True):
+    """Head RMSNorm of q and k (``q_gain``/``k_gain`` None: none), rotation of the first ``rotary_dim`` elements
+    of each q and k head in pairs (i, i + rotary_dim/2), and the cache write, in one pass over the projection's
+    rows.  ``write_cache``: True keys and values go to the cache; False nothing does; ``"keys_in_place"`` the
+    normed, rotated keys go back into the row and the values stay, for a position encoding that works on the
+    row before a second call stores it."""
     _need_cuda(qkv, q_gain, k_gain, inv_freq, row_slot, row_pos, page_table, k_pool, v_pool)
     rows = qkv.shape[0]
     require(qkv.shape[1] == (nq + 2 * nkv) * head_dim, "qk_norm_rope_cache: the projection's width does not fit")
@@ -135,7 +148,7 @@ def qk_norm_rope_cache(qkv, q_gain, k_gain, inv_freq, rotary_dim, row_slot, row_
         _ptr(qkv), _i(_dtype_code(qkv)), _ptr(q_gain), _ptr(k_gain), _i(gain_code), _ptr(inv_freq), _i(rotary_dim),
         _ptr(row_slot), _ptr(row_pos), _ptr(page_table), _i(page_table.shape[1]), _ptr(k_pool), _ptr(v_pool),
         _i(cache_code), _i(page_size), _i(rows), _i(nq), _i(nkv), _i(head_dim), _f(eps),
-        _i(1 if write_cache else 0), _stream()), "qk_norm_rope_cache")
+        _i(2 if write_cache == "keys_in_place" else (1 if write_cache else 0)), _stream()), "qk_norm_rope_cache")
 
 
 def attention_rows(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos, out, nq, nkv, head_dim,

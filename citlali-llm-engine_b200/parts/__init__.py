@@ -1,4 +1,5 @@
-from .base import (BuildContext, StepBatch, part_class, register_part, registered_parts, unregister_part)
+from .base import (BuildContext, StepBatch, build_part, part_class, register_part, registered_parts,
+                   unregister_part)
 from . import rotary, norm, linear, attention, feed_forward, block   # registers the built-in parts
 from .attention import GQAttention
 from .block import PreNormResidualBlock

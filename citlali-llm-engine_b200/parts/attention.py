@@ -22,7 +22,7 @@ from .. import ops
 from ..cache import KVRequirement
 from ..errors import require
 from ..weights.loader import TensorSpec
-from .base import part_class, register_part
+from .base import bind_gain, part_class, register_part
 from .linear import DenseLinear
 
 
@@ -56,7 +56,9 @@ class GQAttention:
         """A step of single tokens reads slots and positions from device memory only: true once bound
         to a dtype and head size that the split-context kernel takes; the other attention kernels size
         their launch from the host's lists."""
-        return getattr(self, "dtype", None) is not None and ops.attention_steps_from_device(self.dtype, self.d)
+        if getattr(self, "dtype", None) is None or not ops.attention_steps_from_device(self.dtype, self.d):
+            return False
+        return self.position.inv_freq is not None or bool(getattr(self.position, "graph_safe", False))
 
     # ---- what it needs ---------------------------------------------------------------
     def tensor_specs(self):
@@ -76,18 +78,21 @@ class GQAttention:
         self.qkv.bind(weights, ctx)
         self.o.bind(weights, ctx)
         if self.eps is not None:
-            def gain(name):
-                g = weights[name].tensor
-                require(tuple(g.shape) == (self.d,),
-                        f"unexpected tensor shape for {name}: got {list(g.shape)}, expected {[self.d]}")
-                return g.to(device=ctx.device, dtype=torch.float32 if ctx.is_float32 else g.dtype).contiguous()
-            self.q_gain = gain(f"{self.prefix}.q_norm.weight")
-            self.k_gain = gain(f"{self.prefix}.k_norm.weight") if self.kv_projection else self.q_gain
+            self.q_gain = bind_gain(weights, f"{self.prefix}.q_norm.weight", self.d, ctx)
+            self.k_gain = (bind_gain(weights, f"{self.prefix}.k_norm.weight", self.d, ctx)
+                           if self.kv_projection else self.q_gain)
             if self.k_gain.dtype != self.q_gain.dtype:
                 self.k_gain = self.k_gain.to(torch.float32)
                 self.q_gain = self.q_gain.to(torch.float32)
-        require(self.position.inv_freq is not None, f"{self.prefix}: this position encoding needs apply()")
-        self.inv_freq = self.position.inv_freq.to(ctx.device)
+        self.fused_position = self.position.inv_freq is not None
+        if self.fused_position:
+            self.rotary_dim = int(self.position.rotary_dim)
+            self.inv_freq = self.position.inv_freq.to(ctx.device)
+        else:
+            require(callable(getattr(self.position, "apply", None)),
+                    f"{self.prefix}: a position encoding gives either inv_freq or apply()")
+            self.rotary_dim = self.d
+            self.inv_freq = torch.zeros(self.d // 2, dtype=torch.float32, device=ctx.device)   # no rotation by the kernel
         self.dtype = ctx.dtype
 
     # ---- one step ----------------------------------------------------------------------
@@ -99,11 +104,19 @@ class GQAttention:
                 f"{self.prefix}: the cache holds {req.num_kv_heads} heads of {req.head_dim}, "
                 f"the layer has {self.nkv} of {self.d}")
         qkv = self.qkv.forward(h)
-        ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.inv_freq, self.position.rotary_dim,
-                               batch.row_slot, batch.row_pos, cache_view.page_table,
-                               cache_view.keys, cache_view.values, cache_view.page_size,
-                               self.nq, nkv_here, self.d, float(self.eps or 0.0),
-                               write_cache=write_cache and self.kv_projection)
+        store = write_cache and self.kv_projection
+        common = (batch.row_slot, batch.row_pos, cache_view.page_table, cache_view.keys, cache_view.values,
+                  cache_view.page_size, self.nq, nkv_here, self.d, float(self.eps or 0.0))
+        if self.fused_position:
+            ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.inv_freq, self.rotary_dim, *common,
+                                   write_cache=store)
+        else:
+            # head norm with the keys kept in the row, the encoding's own work on q and k, then the store
+            ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.inv_freq, self.rotary_dim, *common,
+                                   write_cache="keys_in_place" if store else False)
+            self.position.apply(qkv, batch, self.nq, nkv_here, self.d)
+            if store:
+                ops.qk_norm_rope_cache(qkv, None, None, self.inv_freq, self.rotary_dim, *common, write_cache=True)
         out = torch.empty((batch.rows, self.nq * self.d), dtype=self.dtype, device=h.device)
         ops.attention(qkv, qkv.shape[1], cache_view, batch, out, self.nq, self.nkv, self.d,
                       int(self.window or 0), 1.0 / math.sqrt(self.d))

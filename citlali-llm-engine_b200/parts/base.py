@@ -19,7 +19,8 @@ Interfaces (all tensors are on the model's device; ``x`` is the float32 residual
   position order, ``batch.row_slot`` / ``batch.row_pos`` say whose they are and where.
 * feed-forward: ``forward(h, batch, residual)`` adds its output into ``residual`` in place.
 * position encoding: ``__init__(params, head_dim)``; see :mod:`.rotary`.
-* block: ``__init__(layer_spec)`` builds its parts from the registries;
+* block: ``__init__(layer_spec)`` builds the parts it knows by name from ``layer_spec.parts``
+  (:func:`build_part`); ``parts()``, ``tensor_specs()``, ``cache_requirement()``, ``bind``;
   ``forward(x, batch, cache_view, write_cache)`` updates ``x`` in place.
 """
 from __future__ import annotations
@@ -55,6 +56,11 @@ def part_class(role: str, kind: str) -> type:
 
 def registered_parts(role: str) -> List[str]:
     return sorted(_REGISTRIES[role])
+
+
+def build_part(role: str, spec):
+    """The part a :class:`PartSpec` describes, from the registry of ``role``."""
+    return part_class(role, spec.kind)(spec.params, spec.prefix)
 
 
 @dataclass
@@ -106,3 +112,12 @@ class StepBatch:
     @property
     def max_new(self) -> int:
         return max(self.n_new)
+
+
+def bind_gain(weights, name: str, size: int, ctx: BuildContext) -> torch.Tensor:
+    """A norm's gain on the device: float32 on the 32-bit path and when it is stored in 32-bit (a tensor
+    stored so stays so), else bfloat16 (a float16 gain is rounded once)."""
+    h = weights[name]
+    require(tuple(h.shape) == (size,), f"unexpected tensor shape for {name}: got {list(h.shape)}, expected {[size]}")
+    dtype = torch.float32 if (ctx.is_float32 or h.dtype == torch.float32) else torch.bfloat16
+    return h.tensor.to(device=ctx.device, dtype=dtype).contiguous()

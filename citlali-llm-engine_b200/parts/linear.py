@@ -42,21 +42,24 @@ class DenseLinear:
         return [TensorSpec(n, (o, self.in_features), "matrix") for n, o in zip(self.names, self.out_splits)]
 
     def bind(self, weights, ctx):
-        mats = [weights[n].tensor for n in self.names]
-        for n, m, o in zip(self.names, mats, self.out_splits):
-            require(tuple(m.shape) == (o, self.in_features),
-                    f"unexpected tensor shape for {n}: got {list(m.shape)}, expected {[o, self.in_features]}")
-        mats = [m.to(device=ctx.device, dtype=ctx.dtype) for m in mats]
+        """One device buffer for the stacked matrix; every named matrix is copied straight into its rows
+        (alternating runs if interleaved), converted to the compute dtype on the way."""
+        handles = [weights[n] for n in self.names]
+        for n, h, o in zip(self.names, handles, self.out_splits):
+            require(tuple(h.shape) == (o, self.in_features),
+                    f"unexpected tensor shape for {n}: got {list(h.shape)}, expected {[o, self.in_features]}")
+        w = torch.empty((self.out_features, self.in_features), dtype=ctx.dtype, device=ctx.device)
         if self.interleave_run is not None:
             r = self.interleave_run
-            a = mats[0].view(-1, r, self.in_features)
-            b = mats[1].view(-1, r, self.in_features)
-            w = torch.stack([a, b], dim=1).reshape(self.out_features, self.in_features)
-        elif len(mats) == 1:
-            w = mats[0]
+            runs = w.view(-1, 2, r, self.in_features)          # [run index, gate or up, row in run, in]
+            for k, h in enumerate(handles):
+                h.copy_into(runs[:, k])
         else:
-            w = torch.cat(mats, dim=0)
-        self.weight = w.contiguous()
+            at = 0
+            for h, o in zip(handles, self.out_splits):
+                h.copy_into(w[at:at + o])
+                at += o
+        self.weight = w
         self.dtype = ctx.dtype
         self.error_flag = ctx.error_flag
 

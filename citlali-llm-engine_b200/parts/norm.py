@@ -7,9 +7,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..errors import require
 from ..weights.loader import TensorSpec
-from .base import register_part
+from .base import bind_gain, register_part
 
 
 class RMSNorm:
@@ -25,11 +24,7 @@ class RMSNorm:
         return [TensorSpec(self.name, (self.size,), "gain")]
 
     def bind(self, weights, ctx):
-        g = weights[self.name].tensor
-        require(tuple(g.shape) == (self.size,),
-                f"unexpected tensor shape for {self.name}: got {list(g.shape)}, expected {[self.size]}")
-        # a gain stored in 32-bit stays 32-bit; the 32-bit path widens a bfloat16 gain (exact)
-        self.gain = g.to(device=ctx.device, dtype=torch.float32 if ctx.is_float32 else g.dtype).contiguous()
+        self.gain = bind_gain(weights, self.name, self.size, ctx)
         self.dtype = ctx.dtype
 
     def forward(self, x: torch.Tensor, row_index=None) -> torch.Tensor:

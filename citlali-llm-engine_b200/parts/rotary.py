@@ -7,9 +7,15 @@ The reference evaluates powf on the device for every call; here f_i is tabulated
 host (in double, rounded to float32, which is what a correctly rounded powf returns) and the
 kernels form the angle as the same float32 product and take sincosf of it.
 
-Interface of a position encoding: ``__init__(params, head_dim)``; ``inv_freq`` (float32
-``[rotary_dim/2]`` on the host) if the fused norm-rotate-cache kernel can apply it, else
-``None`` and ``apply(qkv, batch, num_q_heads, num_kv_heads)`` rotates q and k in place.
+Interface of a position encoding: ``__init__(params, head_dim)`` and ``rotary_dim``.  Either
+``inv_freq`` (float32 ``[rotary_dim/2]`` on the host): the fused norm-rotate-cache kernel rotates the
+first ``rotary_dim`` elements of every q and k head in pairs (i, i + rotary_dim/2) by
+``position * inv_freq[i]`` and leaves the rest of the head as it is (``rotary_dim`` below the
+head size: a partial rotation; zero frequencies: none).  Or ``inv_freq = None`` and
+``apply(qkv, batch, num_q_heads, num_kv_heads, head_dim)``, which changes the q and k heads of the
+projection's rows ``[rows, (q + 2 kv heads) * head_dim]`` in place, after their head norm and before the
+keys are stored; ``batch.row_pos`` holds each row's position.  An encoding with ``apply`` says
+``graph_safe = True`` only if it reads positions from the device tensors alone.
 """
 from __future__ import annotations
 

@@ -90,9 +90,26 @@ class SafetensorsFile:
         flat = torch.from_numpy(np.frombuffer(view, dtype=np.uint8).copy())
         return flat.view(dtype).reshape(shape)
 
+    def view(self, name: str) -> torch.Tensor:
+        """The tensor as it lies in the memory map: no copy, read-only, valid until :meth:`close`."""
+        import warnings
+        require(name in self._entries, f"{self.path}: no tensor named '{name}'")
+        dt, shape, begin, end = self._entries[name]
+        dtype = _DTYPES[dt]
+        if end == begin:
+            return torch.empty(shape, dtype=dtype)
+        view = memoryview(self._map)[self._data_start + begin:self._data_start + end]
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")            # torch warns that the buffer cannot be written; it is only read
+            flat = torch.from_numpy(np.frombuffer(view, dtype=np.uint8))
+        return flat.view(dtype).reshape(shape)
+
     def close(self):
         if self._map is not None:
-            self._map.close()
+            try:
+                self._map.close()
+            except BufferError:
+                pass            # a view of the map is still alive somewhere; the map goes when it does
             self._map = None
         self._file.close()
 

@@ -77,11 +77,16 @@ def test_model_spec_is_data():
     spec = cb.config_from_dict(dict(TINY["B"])).to_model_spec()
     assert len(spec.layers) == 3 and [s.layer for s in spec.schedule] == [0, 1, 2]
     layer = spec.layers[1]
-    assert layer.block == "pre_norm_residual" and layer.mixer.kind == "gqa_attention"
-    assert layer.mixer.params["head_dim"] == 32 and layer.mixer.params["qk_norm_eps"] == 1e-5
-    assert layer.mixer.params["position"] == {"kind": "rotary_half_split", "theta": 1e4, "rotary_dim": 32}
-    assert layer.feed_forward.kind == "gated_silu" and layer.feed_forward.params["intermediate_size"] == 160
-    assert layer.mixer.prefix == "model.layers.1.self_attn"
+    assert layer.block == "pre_norm_residual"
+    assert list(layer.parts) == ["mixer_norm", "mixer", "feed_forward_norm", "feed_forward"]
+    mixer, ff = layer.part("mixer"), layer.part("feed_forward")
+    assert mixer.kind == "gqa_attention" and mixer.params["head_dim"] == 32 and mixer.params["qk_norm_eps"] == 1e-5
+    assert mixer.params["position"] == {"kind": "rotary_half_split", "theta": 1e4, "rotary_dim": 32}
+    assert ff.kind == "gated_silu" and ff.params["intermediate_size"] == 160
+    assert mixer.prefix == "model.layers.1.self_attn" and layer.part("mixer_norm").params["eps"] == 1e-5
+    assert spec.embedding_scale is None and spec.logit_scale is None
+    with pytest.raises(cb.CitlaliError, match="needs a part named 'gate'.*mixer_norm, mixer"):
+        layer.part("gate")
 
 
 def test_schedule_validation():
@@ -96,3 +101,18 @@ def test_schedule_validation():
     twice = dataclasses.replace(spec, schedule=(cb.ScheduleStep(0), cb.ScheduleStep(1), cb.ScheduleStep(0),
                                                 cb.ScheduleStep(1, cache_of=1)))
     twice.validate()
+
+
+def test_rope_theta_inside_rope_parameters():
+    """Newer writers of config.json put the rotary base inside a rope_parameters object."""
+    import helpers
+    d = dict(helpers.TINY["B"])
+    theta = d.pop("rope_theta")
+    d["rope_parameters"] = {"rope_type": "default", "rope_theta": theta}
+    assert cb.config_from_dict(d).rope_theta == theta
+    d["rope_parameters"] = {"rope_type": "yarn", "rope_theta": theta, "factor": 4.0}
+    with pytest.raises(cb.CitlaliError, match="rope_type 'yarn'"):
+        cb.config_from_dict(d)
+    d["rope_parameters"] = {"rope_type": "default"}
+    with pytest.raises(cb.CitlaliError, match="rope_theta"):
+        cb.config_from_dict(d)

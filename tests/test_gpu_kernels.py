@@ -188,6 +188,76 @@ def test_qk_norm_rope_cache(nq, nkv, d, page, dtype):
     assert torch.equal(kp2, before_k)
 
 
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(4, 2, 16, 8, 64), (6, 3, 48, 16, 8), (2, 1, 20, 10, 64), (2, 2, 256, 64, 64),
+                                                (3, 1, 128, 2, 16)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_norm_rope_cache_partial_rotation_and_keys_kept_in_the_row(nq, nkv, d, rot, page, dtype):
+    """Only the first `rot` elements of a head are rotated, in pairs (i, i + rot/2); the rest are normed and pass
+    through.  And the two-call form a position encoding with work of its own uses: the first call leaves the normed
+    keys in the row and the cache alone, the second (no gains, zero frequencies) stores keys and values."""
+    g = torch.Generator().manual_seed(d + rot)
+    lengths, slots = [70, 3], [1, 0]
+    rows_pos = [66, 67, 68, 69, 0, 1, 2]
+    rows_slot = [1, 1, 1, 1, 0, 0, 0]
+    M = len(rows_pos)
+    qkv = torch.randn(M, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qg = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype); kg = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype)
+    theta, eps = 1e4, 1e-5
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2 * i / rot).float()
+    empty = [torch.zeros(n, nkv, d) for n in lengths]
+    kp, vp, table = make_paged(empty, empty, lengths, page, dtype, slots_of=slots)
+    kp, vp = kp.to(DEV), vp.to(DEV)
+    before_k, before_v = kp.clone(), vp.clone()
+    slot_t = torch.tensor(rows_slot, dtype=torch.int32, device=DEV)
+    pos_t = torch.tensor(rows_pos, dtype=torch.int32, device=DEV)
+    x = qkv.double()
+    q = x[:, :nq * d].view(M, nq, d); k = x[:, nq * d:(nq + nkv) * d].view(M, nkv, d); v = x[:, (nq + nkv) * d:].view(M, nkv, d)
+
+    def partly_rotated(t, gain):
+        n = plain.head_rms_norm(t, gain.double(), eps)
+        return torch.cat([plain.rotary_half_split(n[..., :rot], rows_pos, theta), n[..., rot:]], dim=-1)
+    q_want, k_want = partly_rotated(q, qg), partly_rotated(k, kg)
+    # one call: rotate part of the head, store
+    dev = qkv.to(DEV).clone()
+    ops.qk_norm_rope_cache(dev, qg.to(DEV), kg.to(DEV), inv_freq.to(DEV), rot, slot_t, pos_t, table.to(DEV), kp, vp, page,
+                           nq, nkv, d, eps)
+    close(dev[:, :nq * d].view(M, nq, d), q_want, dtype)
+    for r in range(M):
+        pg = table[rows_slot[r], rows_pos[r] // page].item(); off = rows_pos[r] % page
+        close(kp[pg, :, off], k_want[r], dtype, scale=float(k_want.abs().max()))
+        assert torch.equal(vp[pg, :, off].cpu(), v[r].to(dtype))
+    # two calls: keys stay in the row first, the cache is written by the second
+    kp2, vp2 = before_k.clone(), before_v.clone()
+    dev2 = qkv.to(DEV).clone()
+    ops.qk_norm_rope_cache(dev2, qg.to(DEV), kg.to(DEV), inv_freq.to(DEV), rot, slot_t, pos_t, table.to(DEV), kp2, vp2, page,
+                           nq, nkv, d, eps, write_cache="keys_in_place")
+    assert torch.equal(kp2, before_k) and torch.equal(vp2, before_v)
+    assert torch.equal(dev2[:, :nq * d], dev[:, :nq * d])
+    close(dev2[:, nq * d:(nq + nkv) * d].view(M, nkv, d), k_want, dtype)
+    assert torch.equal(dev2[:, (nq + nkv) * d:].cpu(), qkv[:, (nq + nkv) * d:])
+    ops.qk_norm_rope_cache(dev2, None, None, torch.zeros(d // 2, device=DEV), d, slot_t, pos_t, table.to(DEV), kp2, vp2, page,
+                           nq, nkv, d, eps)
+    assert torch.equal(kp2, kp) and torch.equal(vp2, vp)
+    with pytest.raises(cb.CitlaliError, match="rotated part"):
+        ops.qk_norm_rope_cache(dev2, None, None, torch.zeros((d + 2) // 2, device=DEV), d + 2, slot_t, pos_t, table.to(DEV),
+                               kp2, vp2, page, nq, nkv, d, eps)
+
+
+def test_embedding_scale_and_logit_scale():
+    table = torch.randn(50, 24)
+    toks = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    plain_rows = torch.empty(3, 24, device=DEV); scaled = torch.empty(3, 24, device=DEV)
+    ops.embed_rows(table.to(DEV), toks, plain_rows, flag)
+    ops.embed_rows(table.to(DEV), toks, scaled, flag, scale=4.5)
+    assert torch.equal(plain_rows.cpu(), table[[3, 49, 0]]) and torch.equal(scaled.cpu(), table[[3, 49, 0]] * 4.5)
+    x = torch.randn(7, 1001, device=DEV)
+    y = x.clone()
+    ops.scale_(y, 0.125)
+    assert torch.equal(y, x * 0.125)
+
+
 def test_head_sizes_are_taken_or_refused():
     with pytest.raises(cb.CitlaliError, match="head size"):
         z = torch.zeros(1, 3 * 258, device=DEV)

@@ -89,6 +89,36 @@ ATTN = {"hidden_size": 40, "num_heads": 6, "num_kv_heads": 2, "head_dim": 48, "q
         "position": {"kind": "rotary_half_split", "theta": 3e4, "rotary_dim": 48}, "window": None}
 
 
+class InterleavedRotary:
+    """A position encoding defined here, with work of its own: pairs (2i, 2i + 1) of every q and k head are rotated
+    by position * theta^(-2i/d).  It gives no frequency table, so the attention part calls ``apply``."""
+    inv_freq = None
+
+    def __init__(self, params, head_dim):
+        self.theta, self.rotary_dim = float(params["theta"]), head_dim
+
+    def apply(self, qkv, batch, num_q_heads, num_kv_heads, head_dim):
+        rows = qkv.shape[0]
+        heads = qkv[:, :(num_q_heads + num_kv_heads) * head_dim].view(rows, num_q_heads + num_kv_heads, head_dim // 2, 2)
+        i = torch.arange(head_dim // 2, dtype=torch.float64, device=qkv.device)
+        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64, device=qkv.device), -2.0 * i / head_dim).float()
+        angle = batch.row_pos.float()[:, None] * inv[None, :]
+        c, s_ = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        a, b = heads[..., 0].float(), heads[..., 1].float()
+        heads[..., 0], heads[..., 1] = (a * c - b * s_).to(qkv.dtype), (a * s_ + b * c).to(qkv.dtype)
+
+
+def plain_interleaved_rotary(t, positions, theta):
+    d = t.shape[-1]
+    i = torch.arange(d // 2, dtype=torch.float64)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / d).to(torch.float32)
+    ang = (torch.tensor(positions, dtype=torch.float32)[:, None] * inv[None, :]).double()
+    c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    pairs = t.reshape(*t.shape[:-1], d // 2, 2)
+    a, b = pairs[..., 0], pairs[..., 1]
+    return torch.stack([a * c - b * s_, a * s_ + b * c], dim=-1).reshape(t.shape)
+
+
 def plain_attention_part(x, w, params, window=None, qk_norm=True, rotate=True):
     T = x.shape[0]
     nq, nkv, d = params["num_heads"], params["num_kv_heads"], params["head_dim"]
@@ -98,18 +128,29 @@ def plain_attention_part(x, w, params, window=None, qk_norm=True, rotate=True):
     if qk_norm:
         q = plain.head_rms_norm(q, w["a.q_norm.weight"], params["qk_norm_eps"])
         k = plain.head_rms_norm(k, w["a.k_norm.weight"], params["qk_norm_eps"])
-    if rotate:
-        q = plain.rotary_half_split(q, list(range(T)), params["position"]["theta"])
-        k = plain.rotary_half_split(k, list(range(T)), params["position"]["theta"])
+    if rotate == "interleaved":
+        q = plain_interleaved_rotary(q, list(range(T)), params["position"]["theta"])
+        k = plain_interleaved_rotary(k, list(range(T)), params["position"]["theta"])
+    elif rotate:
+        r = params["position"].get("rotary_dim", d)           # the first r elements of a head are rotated
+        theta = params["position"]["theta"]
+        q = torch.cat([plain.rotary_half_split(q[..., :r], list(range(T)), theta), q[..., r:]], dim=-1)
+        k = torch.cat([plain.rotary_half_split(k[..., :r], list(range(T)), theta), k[..., r:]], dim=-1)
     o = plain.causal_attention(q, k, v, nq, nkv, window=window).reshape(T, nq * d)
     return plain.linear(o, w["a.o_proj.weight"])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("variant", ["plain", "window", "no_norm_no_rotation"])
+@pytest.mark.parametrize("variant", ["plain", "window", "no_norm_no_rotation", "partial_rotation", "position_with_apply"])
 def test_attention_part_whole_and_token_by_token(dtype, variant):
     params = dict(ATTN)
     kwargs = {}
+    if variant == "partial_rotation":
+        params["position"] = {"kind": "rotary_half_split", "theta": 3e4, "rotary_dim": 16}
+    if variant == "position_with_apply":
+        cb.register_part("position", "interleaved_rotary", InterleavedRotary, replace=True)
+        params["position"] = {"kind": "interleaved_rotary", "theta": 3e4}
+        kwargs["rotate"] = "interleaved"
     if variant == "window":
         params["window"] = 9; kwargs["window"] = 9
     if variant == "no_norm_no_rotation":
@@ -144,12 +185,11 @@ def test_attention_part_whole_and_token_by_token(dtype, variant):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_block_part(dtype):
-    spec = cb.LayerSpec(
-        block="pre_norm_residual",
-        mixer=cb.PartSpec("gqa_attention", dict(ATTN), "a"),
-        feed_forward=cb.PartSpec("gated_silu", {"hidden_size": 40, "intermediate_size": 48}, "mlp"),
-        mixer_norm=cb.PartSpec("rms_norm", {"size": 40, "eps": 1e-5}, "n1"),
-        feed_forward_norm=cb.PartSpec("rms_norm", {"size": 40, "eps": 2e-5}, "n2"))
+    spec = cb.LayerSpec(block="pre_norm_residual", parts={
+        "mixer_norm": cb.PartSpec("rms_norm", {"size": 40, "eps": 1e-5}, "n1"),
+        "mixer": cb.PartSpec("gqa_attention", dict(ATTN), "a"),
+        "feed_forward_norm": cb.PartSpec("rms_norm", {"size": 40, "eps": 2e-5}, "n2"),
+        "feed_forward": cb.PartSpec("gated_silu", {"hidden_size": 40, "intermediate_size": 48}, "mlp")})
     block = part_class("block", "pre_norm_residual")(spec)
     h, w = handles(block, dtype)
     block.bind(h, ctx_for(dtype))

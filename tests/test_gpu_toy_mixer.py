@@ -66,13 +66,12 @@ class ToyConfig:
         ff = lambda p: cb.PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 2 * H}, p)
         attn = {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qk_norm_eps": 1e-5,
                 "position": {"kind": "rotary_half_split", "theta": 1e4, "rotary_dim": 16}, "window": None}
+        layer = lambda l, mixer: cb.LayerSpec("pre_norm_residual", {
+            "mixer_norm": norm(f"l{l}.n1"), "mixer": mixer, "feed_forward_norm": norm(f"l{l}.n2"), "feed_forward": ff(f"l{l}.mlp")})
         layers = (
-            cb.LayerSpec("pre_norm_residual", cb.PartSpec("running_mean", {"hidden_size": H}, "l0.mix"),
-                         ff("l0.mlp"), norm("l0.n1"), norm("l0.n2")),
-            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", attn, "l1.attn"),
-                         ff("l1.mlp"), norm("l1.n1"), norm("l1.n2")),
-            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", dict(attn, kv_projection=False), "l2.attn"),
-                         ff("l2.mlp"), norm("l2.n1"), norm("l2.n2")),
+            layer(0, cb.PartSpec("running_mean", {"hidden_size": H}, "l0.mix")),
+            layer(1, cb.PartSpec("gqa_attention", attn, "l1.attn")),
+            layer(2, cb.PartSpec("gqa_attention", dict(attn, kv_projection=False), "l2.attn")),
         )
         # layer 0 runs twice (two states of its own); layer 2 has no keys and reads layer 1's
         schedule = (cb.ScheduleStep(0), cb.ScheduleStep(1), cb.ScheduleStep(0), cb.ScheduleStep(2, cache_of=1))
@@ -175,9 +174,11 @@ class RoutedConfig:
         routed = cb.PartSpec("top1_routed", {"hidden_size": H, "intermediate_size": 48, "experts": 3}, "l0.moe")
         dense = cb.PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 96}, "l1.mlp")
         layers = (
-            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", attn, "l0.attn"), routed, norm("l0.n1"), norm("l0.n2")),
-            cb.LayerSpec("pre_norm_residual", cb.PartSpec("gqa_attention", dict(attn, window=None), "l1.attn"), dense,
-                         norm("l1.n1"), norm("l1.n2")),
+            cb.LayerSpec("pre_norm_residual", {"mixer_norm": norm("l0.n1"), "mixer": cb.PartSpec("gqa_attention", attn, "l0.attn"),
+                                               "feed_forward_norm": norm("l0.n2"), "feed_forward": routed}),
+            cb.LayerSpec("pre_norm_residual", {"mixer_norm": norm("l1.n1"),
+                                               "mixer": cb.PartSpec("gqa_attention", dict(attn, window=None), "l1.attn"),
+                                               "feed_forward_norm": norm("l1.n2"), "feed_forward": dense}),
         )
         return cb.ModelSpec("ToyRoutedForCausalLM", self.vocab_size, H, self.max_position_embeddings, "emb.weight",
                             layers, (cb.ScheduleStep(0), cb.ScheduleStep(1)), norm("final"), "head.weight", None)

@@ -125,3 +125,49 @@ def test_missing_files(tmp_path):
         cb.config_from_model_dir(str(tmp_path))
     with pytest.raises(cb.CitlaliError, match="no model.safetensors"):
         cb.WeightLoader(str(tmp_path))
+
+
+def test_handles_read_on_demand_and_fill_buffers_in_place(tmp_path):
+    """A handle holds no values; ``tensor`` reads a copy, ``copy_into`` fills a buffer of another dtype or a
+    strided view of a larger one (how stacked and interleaved matrices are bound)."""
+    d = make_model_dir(str(tmp_path / "m"), "B", "bfloat16")
+    loader = cb.WeightLoader(d)
+    w = loader.load_all(cb.expected_tensors(tiny_config("B").to_model_spec()))
+    h = w["model.layers.0.mlp.gate_proj.weight"]
+    assert h.dtype == torch.bfloat16 and h.shape == (160, 96) and h.nbytes == 160 * 96 * 2
+    a, b = h.tensor, h.tensor
+    assert a.data_ptr() != b.data_ptr() and torch.equal(a, b)           # nothing is kept behind the handle
+    wide = torch.zeros(160, 96, dtype=torch.float32)
+    h.copy_into(wide)
+    assert torch.equal(wide, a.float())
+    stacked = torch.zeros(10, 2, 16, 96, dtype=torch.bfloat16)           # runs of 16 rows, gate and up alternating
+    h.copy_into(stacked[:, 0])
+    w["model.layers.0.mlp.up_proj.weight"].copy_into(stacked[:, 1])
+    flat = stacked.view(320, 96)
+    assert torch.equal(flat[0:16], a[0:16]) and torch.equal(flat[32:48], a[16:32])
+    assert torch.equal(flat[16:32], w["model.layers.0.mlp.up_proj.weight"].tensor[0:16])
+    with pytest.raises(cb.CitlaliError, match="elements"):
+        h.copy_into(torch.zeros(10, 10))
+    loader.close()
+
+
+def test_float16_checkpoints_reach_the_32_bit_path_exactly(tmp_path):
+    d = make_model_dir(str(tmp_path / "m"), "A", "float32")
+    halves = {}
+
+    def change(t):
+        for k in list(t):
+            t[k] = t[k].to(torch.float16)
+            halves[k] = t[k].clone()
+    _rewrite(d, change)
+    loader = cb.WeightLoader(d)
+    w = loader.load_all(cb.expected_tensors(tiny_config("A").to_model_spec()))
+    h = w["model.layers.1.self_attn.o_proj.weight"]
+    assert h.dtype == torch.float16
+    wide = torch.zeros(h.shape, dtype=torch.float32)
+    h.copy_into(wide)
+    assert torch.equal(wide, halves[h.name].float())                     # no bits lost on the way to 32-bit
+    narrow = torch.zeros(h.shape, dtype=torch.bfloat16)
+    h.copy_into(narrow)
+    assert torch.equal(narrow, halves[h.name].to(torch.bfloat16))        # one rounding on the way to bfloat16
+    loader.close()
