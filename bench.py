@@ -4,12 +4,17 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 3|4 [--repetitions R]      the batch workloads of BASELINE.json's other shapes
 
-Prints ONE JSON line.  ``value`` is decoded tokens a second at batch 8 with every sequence
-near the context length of the benchmark configuration (device time, CUDA events around K
-replayed decode steps); ``e2e`` is the same through ``InferenceSession.decode`` with the
-step's tokens coming from pinned host memory and the sampled tokens read back every step.
-``prefill`` times one 2,048-token prompt; ``roofline`` relates the decode step to the bytes it
-must read; ``points`` give decode at batch 1 and 64.  Several GPUs are not supported.
+Prints ONE JSON line.  For each batch size (8, and 1 and 64 unless --skip-points) the run is a real one: the
+prompts (2,048 random tokens each) are prefilled in one step, then every sequence is decoded token by token up
+to the context length (4,096) through the replayed decode step, each step fed on the device with the tokens
+the step before sampled; CUDA events give the rate over the whole run and over windows of 64 steps at contexts
+2,048, 3,072 and 4,096 (``points``).  ``value`` is decoded tokens a second at batch 8 over the last K steps
+before the context length (the sequences are rewound and those W + K steps run again: the median of
+``repetitions`` timings); ``e2e`` is the same steps through ``InferenceSession.decode`` with the step's tokens
+coming from host memory and the sampled tokens read back every step.  ``prefill`` times one 2,048-token prompt
+(``frac``: the matrix products' FLOPs over the time over the bf16 peak); ``roofline`` relates the decode step
+to the bytes it must read; ``kernels`` times the kernels of a layer one kind at a time.  Several GPUs are not
+supported.
 """
 import argparse
 import json
@@ -313,10 +318,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true", help="batch 8 only, no per-kernel timings")
     ap.add_argument("--workload", type=int, default=2,
                     help="which of BASELINE.json's configs to run: 2 (the benchmark configuration) or a batch workload (3, 4)")
-    ap.add_argument("--repetitions", type=int, default=5, help="timed runs of a batch workload (the median is reported)")
+    ap.add_argument("--repetitions", type=int, default=5, help="timed repetitions (the median is reported)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -336,7 +341,7 @@ def main():
     layers_full = shape["num_hidden_layers"]
     layers = args.layers or layers_full
     context, prefill_tokens = shape["context"], shape["prefill_tokens"]
-    K, W = args.steps, max(args.warmup, 3)
+    K, W, R = args.steps, max(args.warmup, 3), max(1, args.repetitions)
     cfg = cb.config_from_dict(dict(
         architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=shape["hidden_size"],
         num_attention_heads=shape["num_attention_heads"], num_key_value_heads=shape["num_key_value_heads"],
@@ -344,12 +349,10 @@ def main():
         rope_theta=shape["rope_theta"], rms_norm_eps=shape["rms_norm_eps"],
         tie_word_embeddings=shape["tie_word_embeddings"], max_position_embeddings=max(context, 40960)))
     pk = peaks()
-    max_batch = 64 if not args.skip_points else args.batch
+    batches = [args.batch] if args.skip_points else sorted({args.batch, 1, 64})
     t_load = time.time()
     session = cb.InferenceSession().load_random(cfg, seed=1, max_context=context, dtype="bfloat16", device="cuda:0",
-                                                max_batch=max_batch)
-    for g in session.cache.kv_groups:            # keys and values of the assumed context: synthetic
-        g.keys.normal_(0.0, 0.5); g.values.normal_(0.0, 0.5)
+                                                max_batch=max(batches))
     torch.cuda.synchronize()
     print(f"[bench] model of {layers} layers ready in {time.time() - t_load:.0f} s", file=sys.stderr, flush=True)
     vocab = cfg.vocab_size
@@ -360,11 +363,14 @@ def main():
     weight_bytes = session.model.weight_bytes_read_per_step()
     kv_bytes_per_token = sum(2 * g.requirement.num_kv_heads * g.requirement.head_dim * 2 * len(g.steps)
                              for g in session.cache.kv_groups)
+    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I
 
     # ---- prefill: one prompt of 2,048 tokens ----------------------------------------------
     prompt = [rng.randrange(vocab) for _ in range(prefill_tokens)]
     times = []
-    for i in range(3 + 3):
+    for i in range(3 + R):
         slot = session.acquire()
         a, b = ev(), ev()
         torch.cuda.synchronize()
@@ -377,97 +383,240 @@ def main():
         if i >= 3:
             times.append(a.elapsed_time(b))
     prefill_ms = statistics.median(times)
-    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
-    nq, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
-    layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I
     T = prefill_tokens
-    prefill_flops = 2.0 * T * layer_params * layers + 2.0 * H * vocab + layers * 4.0 * (T * (T + 1) / 2) * d * nq
-    prefill = {"value": T / (prefill_ms / 1e3), "tokens": T, "ms": prefill_ms,
-               "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "tflops": prefill_flops / (prefill_ms / 1e3) / 1e12}
+    gemm_flops = 2.0 * T * layer_params * layers + 2.0 * H * vocab
+    attention_flops = layers * 4.0 * (T * (T + 1) / 2) * d * nq
+    per_s = 1.0 / (prefill_ms / 1e3)
+    prefill = {"value": T * per_s, "tokens": T, "ms": prefill_ms,
+               "frac": gemm_flops * per_s / (pk["bf16_tflops"] * 1e12),
+               "frac_counts": "matrix products only (the metric's definition), of the burst peak",
+               "frac_with_attention": (gemm_flops + attention_flops) * per_s / (pk["bf16_tflops"] * 1e12),
+               "tflops": gemm_flops * per_s / 1e12, "repetitions": R}
     if "bf16_tflops_sustained" in pk:
-        prefill["frac_sustained"] = prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12)
+        prefill["frac_sustained"] = gemm_flops * per_s / (pk["bf16_tflops_sustained"] * 1e12)
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
-    # ---- decode -----------------------------------------------------------------------------
-    def decode_run(batch, steps, warm, end_to_end):
-        """Tokens a second, ms a step, kernels launched and the mean cached length, over `steps`
-        decode steps that end at the context length."""
-        start_len = context - (warm + steps) - 1
+    # ---- decode: a run from the prompts' end to the context length, then the last steps again ----------
+    runner = session.runner
+
+    def step_bytes(batch, mean_len):
+        return weight_bytes + batch * mean_len * kv_bytes_per_token
+
+    def decode_run(batch):
         slots = [session.acquire() for _ in range(batch)]
-        for s in slots:
-            session.assume_cached(s, start_len)
-        tokens = [rng.randrange(vocab) for _ in range(batch)]
+        prompts = [[rng.randrange(vocab) for _ in range(prefill_tokens)] for _ in range(batch)]
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        first = session.prefill(slots, prompts, 0.0, [])
+        b.record()
+        torch.cuda.synchronize()
+        out = {"prefill_ms": a.elapsed_time(b)}
+        total = context - prefill_tokens                       # decode steps: positions prefill_tokens .. context-1
+        window = min(64, total // 4)
+        marks = {"ctx%d" % prefill_tokens: 0, "ctx%d" % ((prefill_tokens + context) // 2): total // 2 - window // 2,
+                 "ctx%d" % context: total - window}
+        starts = {max(at, 1): name for name, at in marks.items()}
+        ends = {max(at, 1) + window - 1: name for name, at in marks.items()}
+        events = {name: [ev(), ev()] for name in marks}
+        runner.launch(slots, first, 0.0, [])                   # step 0 (captures the graph on first use)
+        torch.cuda.synchronize()
         launches = 0
-        if end_to_end:
-            for _ in range(warm):
-                tokens = session.decode(slots, tokens, 0.0, [])
-            torch.cuda.synchronize()
-            before = ops.launch_count()
-            t0 = time.perf_counter()
-            for _ in range(steps):
-                tokens = session.decode(slots, tokens, 0.0, [])
-            torch.cuda.synchronize()
-            seconds = time.perf_counter() - t0
-            launches = steps * session.runner.kernels_per_replay[(batch, True)] + ops.launch_count() - before
-        else:
-            runner = session.runner
-            runner.launch(slots, tokens, 0.0, [])
-            for _ in range(warm - 1):
-                runner.feed_back(batch)
-                runner.launch(slots, None, 0.0, [])
+        start = ev(); start.record()
+        for step in range(1, total):
+            if step in starts:
+                events[starts[step]][0].record()
+            runner.feed_back(batch)
+            launches = runner.launch(slots, None, 0.0, [])
+            if step in ends:
+                events[ends[step]][1].record()
+        end = ev(); end.record()
+        torch.cuda.synchronize()
+        session.check_device_errors()
+        out["run_tok_s"] = batch * (total - 1) / (start.elapsed_time(end) / 1e3)
+        for name, (e0, e1) in events.items():
+            out[name] = batch * window / (e0.elapsed_time(e1) / 1e3)
+        # the last W + K steps again, R times on the device and R times end to end
+        def rewind():
+            for s in slots:
+                session.cache.rewind(s, context - (W + K))
+        dev_ms, e2e_ms = [], []
+        for _ in range(R):
+            rewind()
+            runner.launch(slots, first, 0.0, [])
+            for _ in range(W - 1):
+                runner.feed_back(batch); runner.launch(slots, None, 0.0, [])
             a, b = ev(), ev()
             torch.cuda.synchronize()
             a.record()
-            for _ in range(steps):
-                runner.feed_back(batch)
-                launches += runner.launch(slots, None, 0.0, [])
+            for _ in range(K):
+                runner.feed_back(batch); runner.launch(slots, None, 0.0, [])
             b.record()
             torch.cuda.synchronize()
-            seconds = a.elapsed_time(b) / 1e3
+            dev_ms.append(a.elapsed_time(b) / K)
+        for _ in range(R):
+            rewind()
+            tokens = list(first)
+            for _ in range(W):
+                tokens = session.decode(slots, tokens, 0.0, [])
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                tokens = session.decode(slots, tokens, 0.0, [])
+            torch.cuda.synchronize()
+            e2e_ms.append((time.perf_counter() - t0) / K * 1e3)
         session.check_device_errors()
-        mean_len = start_len + warm + (steps - 1) / 2.0 + 1
         for s in slots:
             session.release(s)
-        return {"tok_s": batch * steps / seconds, "ms": seconds / steps * 1e3, "launches": launches, "mean_len": mean_len}
+        out.update(ms=statistics.median(dev_ms), e2e_ms=statistics.median(e2e_ms), launches=launches,
+                   mean_len=context - (K - 1) / 2.0)
+        out["tok_s"] = batch / (out["ms"] / 1e3)
+        out["e2e_tok_s"] = batch / (out["e2e_ms"] / 1e3)
+        out["frac"] = step_bytes(batch, out["mean_len"]) / (out["ms"] / 1e3) / 1e9 / pk["hbm_gbs"]
+        return out
 
-    main_run = decode_run(args.batch, K, W, False)
-    print(f"[bench] decode b{args.batch} {main_run}", file=sys.stderr, flush=True)
-    e2e_run = decode_run(args.batch, K, W, True)
-    print(f"[bench] e2e b{args.batch} {e2e_run}", file=sys.stderr, flush=True)
-    points = {}
-    if not args.skip_points:
-        for b in (1, 64):
-            r = decode_run(b, min(K, 32), W, False)
-            points[f"decode_b{b}"] = r["tok_s"]
-            print(f"[bench] decode b{b} {r}", file=sys.stderr, flush=True)
+    runs = {}
+    for bsz in batches:
+        runs[bsz] = decode_run(bsz)
+        print(f"[bench] decode b{bsz} {runs[bsz]}", file=sys.stderr, flush=True)
+    main_run = runs[args.batch]
+    points, point_fracs = {}, {}
+    for bsz, r in runs.items():
+        if bsz != args.batch:
+            points[f"decode_b{bsz}"] = r["tok_s"]
+            point_fracs[f"decode_b{bsz}"] = round(r["frac"], 4)
+        for name, v in r.items():
+            if name.startswith("ctx"):
+                points[f"decode_b{bsz}_{name}"] = v
+                ctx_len = int(name[3:]) + (32 if int(name[3:]) < context else -32)
+                point_fracs[f"decode_b{bsz}_{name}"] = round(step_bytes(bsz, ctx_len) * v / bsz / 1e9 / pk["hbm_gbs"], 4)
+        points[f"decode_b{bsz}_run"] = r["run_tok_s"]
+        points[f"prefill_b{bsz}_tok_s"] = bsz * prefill_tokens / (r["prefill_ms"] / 1e3)
+
+    kernels = {} if args.skip_points else time_kernels(session, cb, ops, torch, cfg, args.batch, context, prefill_tokens, pk)
     clock_record = clocks.stop()
 
-    step_bytes = weight_bytes + args.batch * main_run["mean_len"] * kv_bytes_per_token
-    achieved = step_bytes / (main_run["ms"] / 1e3) / 1e9
-    runner = session.runner
+    bytes_main = step_bytes(args.batch, main_run["mean_len"])
+    achieved = bytes_main / (main_run["ms"] / 1e3) / 1e9
     h2d = int(runner._offsets[6] * 4)
     line = {
-        "metric": "decode tok/s @ batch 8 (Qwen3-8B shape, random bf16 weights)",
+        "metric": f"decode tok/s @ batch {args.batch} (Qwen3-8B shape, random bf16 weights)",
         "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": main_run["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids, cache of the assumed context filled with random keys and values",
-        "impl": "ours",
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), prompts of uniform random token ids prefilled for real, "
+                                 "decoded tokens fed back",
+        "impl": "ours", "repetitions": R,
         "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": layers_full, "hidden": H,
                    "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": vocab,
                    "global_batch": args.batch, "seq_len": context, "prefill_tokens": prefill_tokens,
                    "parallelism": "single GPU", "l2": "inputs larger than L2: every step reads all weights",
                    "peaks": pk["source"]},
-        "e2e": {"value": e2e_run["tok_s"], "unit": "tok/s", "ms_per_step": e2e_run["ms"],
+        "e2e": {"value": main_run["e2e_tok_s"], "unit": "tok/s", "ms_per_step": main_run["e2e_ms"],
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": main_run["launches"],
+        "gpu_launches": K * main_run["launches"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": step_bytes},
+                     "frac": achieved / pk["hbm_gbs"], "bytes_per_step": bytes_main},
         "points": points,
+        "points_roofline_frac": point_fracs,
+        "kernels": kernels,
         "clocks": clock_record,
     }
     print(json.dumps(line))
     return 0
+
+
+def time_kernels(session, cb, ops, torch, cfg, batch, context, prefill_tokens, pk):
+    """The kernels of a layer, one kind at a time: the same kernel on every layer's own weights and cache in
+    turn (15 GB of weights between two uses of the same bytes, far more than L2 holds), the sweep captured in a
+    CUDA graph and replayed, CUDA events around the replay, the mean per launch.  Decode at `batch` sequences of `context` - 1 cached tokens, and one prompt of
+    `prefill_tokens` tokens.  Fractions: bytes the kernel must read over the time over the copy bandwidth
+    (decode), FLOPs over the time over the bf16 burst peak (prompt)."""
+    import math
+    model, cache = session.model, session.cache
+    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.vocab_size
+    dev = model.ctx.device
+    blocks = [model.layers[s.layer] for s in model.spec.schedule]
+    out = {}
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def sweep(fn, count=len(blocks), rounds=3):
+        # the sweep is captured once and replayed, so that no launch waits for the host
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn(0)                                      # outside capture first: kernel attributes, scratch buffers
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(count):
+                fn(i)
+        best = None
+        for _ in range(rounds + 1):
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            t = a.elapsed_time(b) * 1e3 / count
+            best = t if best is None else min(best, t)
+        return best
+
+    for what, rows, past in (("decode", batch, context - 1), ("prefill", prefill_tokens, 0)):
+        nseq = batch if what == "decode" else 1
+        slots = [session.acquire() for _ in range(nseq)]
+        for s in slots:
+            session.assume_cached(s, past + rows // nseq)
+        entries = [cb.StepEntry(s, [0] * (rows // nseq), []) for s in slots]
+        from citlali_b200.engine.step import pack_step
+        step = pack_step(entries, [past] * nseq, V, dev)
+        h = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+        x = torch.zeros(rows, H, dtype=torch.float32, device=dev)
+        act = torch.randn(rows, I, device=dev).to(torch.bfloat16)
+        o_in = torch.randn(rows, nq * d, device=dev).to(torch.bfloat16)
+        qkv = torch.randn(rows, (nq + 2 * nkv) * d, device=dev).to(torch.bfloat16)
+        attn_out = torch.empty(rows, nq * d, dtype=torch.bfloat16, device=dev)
+        views = [cache.view(i) for i in range(len(blocks))]
+        m = [b.mixer for b in blocks]
+        f = [b.feed_forward for b in blocks]
+        us = {
+            "norm": sweep(lambda i: blocks[i].mixer_norm.forward(x)),
+            "qkv": sweep(lambda i: m[i].qkv.forward(h)),
+            "norm_rope_cache": sweep(lambda i: ops.qk_norm_rope_cache(
+                qkv, m[i].q_gain, m[i].k_gain, m[i].inv_freq, m[i].rotary_dim, step.row_slot, step.row_pos, views[i].page_table,
+                views[i].keys, views[i].values, views[i].page_size, nq, nkv, d, float(m[i].eps))),
+            "attention": sweep(lambda i: ops.attention(qkv, qkv.shape[1], views[i], step, attn_out, nq, nkv, d, 0,
+                                                       1.0 / math.sqrt(d))),
+            "output": sweep(lambda i: m[i].o.forward(o_in, accumulate_into=x)),
+            "gate_up": sweep(lambda i: f[i].gate_up.forward_gated(h, f[i].run)),
+            "down": sweep(lambda i: f[i].down.forward(act, accumulate_into=x)),
+        }
+        if what == "decode":
+            hw = torch.randn(batch, H, device=dev).to(torch.bfloat16)
+            us["head"] = sweep(lambda i: model.head.forward(hw, out_dtype=torch.float32), count=4)
+        for s in slots:
+            session.release(s)
+        keys = rows // nseq + past
+        if what == "decode":
+            need = {"qkv": 2.0 * (nq + 2 * nkv) * d * H, "attention": 2.0 * 2 * nseq * keys * nkv * d, "output": 2.0 * H * nq * d,
+                    "gate_up": 2.0 * 2 * I * H, "down": 2.0 * H * I, "head": 2.0 * V * H}
+            for k, t in us.items():
+                out[f"decode_{k}"] = {"us": round(t, 2)}
+                if k in need:
+                    out[f"decode_{k}"]["frac"] = round(need[k] / (t * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+        else:
+            need = {"qkv": 2.0 * rows * (nq + 2 * nkv) * d * H, "attention": 4.0 * (rows * (rows + 1) / 2) * d * nq,
+                    "output": 2.0 * rows * H * nq * d, "gate_up": 2.0 * rows * 2 * I * H, "down": 2.0 * rows * H * I}
+            for k, t in us.items():
+                out[f"prefill_{k}"] = {"us": round(t, 1)}
+                if k in need:
+                    out[f"prefill_{k}"]["frac"] = round(need[k] / (t * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+    out["note"] = ("us per launch in a replayed sweep over the layers, best of 4; decode frac = bytes the kernel must read / time / "
+                   "copy bandwidth, prefill frac = FLOPs / time / bf16 burst peak")
+    return out
 
 
 if __name__ == "__main__":

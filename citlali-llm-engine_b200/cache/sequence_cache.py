@@ -202,6 +202,15 @@ class SequenceCache:
             if gone:
                 g.pages.free([g.held[slot].pop(i) for i in gone])
 
+    def rewind(self, slot: int, new_length: int) -> None:
+        """Forget a sequence's tokens from ``new_length`` on (they will be computed again or replaced).
+        Pages stay with the slot.  Not for caches with a window group, whose early pages are already gone."""
+        require(self.slots.is_held(slot), f"slot {slot} is not held")
+        require(0 <= new_length <= self.lengths[slot],
+                f"slot {slot} holds {self.lengths[slot]} tokens and cannot be rewound to {new_length}")
+        require(not self._has_window, "a cache with a windowed group cannot be rewound")
+        self.lengths[slot] = new_length
+
     # ---- what layers see ---------------------------------------------------------------
     def view(self, step: int):
         require(step in self._where, f"schedule step {step} keeps no cache")

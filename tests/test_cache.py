@@ -143,3 +143,23 @@ def test_random_traffic_keeps_the_books():
         for s, n in live.items():
             assert c.length(s) == n
             assert set(range((n + 63) // 64)) == set(c.kv_groups[0].held[s])
+
+
+def test_rewind_keeps_pages_and_lowers_the_length():
+    import torch
+    from citlali_b200.cache import KVRequirement, SequenceCache
+    c = SequenceCache([KVRequirement(2, 16)], 2, 64 * 8, 64 * 4, torch.float32, "cpu")
+    s = c.acquire()
+    c.reserve(s, 200); c.commit(s, 200)
+    held = c.pages_held()
+    c.rewind(s, 70)
+    assert c.length(s) == 70 and c.pages_held() == held
+    c.reserve(s, 200); c.commit(s, 200)
+    assert c.pages_held() == held
+    with pytest.raises(cb.CitlaliError, match="cannot be rewound"):
+        c.rewind(s, 201)
+    w = SequenceCache([KVRequirement(2, 16, window=32)], 1, 64 * 8, 64 * 4, torch.float32, "cpu")
+    t = w.acquire()
+    w.reserve(t, 100); w.commit(t, 100)
+    with pytest.raises(cb.CitlaliError, match="windowed"):
+        w.rewind(t, 50)
