@@ -588,8 +588,14 @@ def time_kernels(session, cb, ops, torch, cfg, batch, context, prefill_tokens, p
             "norm_rope_cache": sweep(lambda i: ops.qk_norm_rope_cache(
                 qkv, m[i].q_gain, m[i].k_gain, m[i].inv_freq, m[i].rotary_dim, step.row_slot, step.row_pos, views[i].page_table,
                 views[i].keys, views[i].values, views[i].page_size, nq, nkv, d, float(m[i].eps))),
-            "attention": sweep(lambda i: ops.attention(qkv, qkv.shape[1], views[i], step, attn_out, nq, nkv, d, 0,
-                                                       1.0 / math.sqrt(d))),
+            # (the prompt kernel is called by name: inside a captured sweep the choice between kernels refuses the ones
+            # whose launch depends on the step's lengths, which here are constants)
+            "attention": sweep((lambda i: ops.attention(qkv, qkv.shape[1], views[i], step, attn_out, nq, nkv, d, 0,
+                                                        1.0 / math.sqrt(d))) if what == "decode" else
+                               (lambda i: ops.attention_prefill_tc(qkv, qkv.shape[1], views[i].keys, views[i].values,
+                                                                   views[i].page_table, step.seq_start, step.seq_slot, step.seq_past,
+                                                                   attn_out, 1, rows, nq, nkv, d, views[i].page_size, 0,
+                                                                   1.0 / math.sqrt(d), model.ctx.error_flag))),
             "output": sweep(lambda i: m[i].o.forward(o_in, accumulate_into=x)),
             "gate_up": sweep(lambda i: f[i].gate_up.forward_gated(h, f[i].run)),
             "down": sweep(lambda i: f[i].down.forward(act, accumulate_into=x)),

@@ -6,21 +6,32 @@
 // number of heads), else two consecutive row tiles of one head.  It walks the visible keys 128 at
 // a time (two cache pages); each key and value tile is fetched once for both query tiles, which
 // halves the traffic from L2, the resource this kernel is otherwise bound by.  Roles:
-//   warps 8, 9, one lane each: TMA producers of the key and of the value tiles (128-byte swizzle; a
+//   warps 16, 17, one lane each: TMA producers of the key and of the value tiles (128-byte swizzle; a
 //                     tile is two 64-wide halves of the head), two tiles deep.
-//   warp 10, one lane: MMA issuer for both query tiles.  S = Q K^T (tcgen05.mma, both operands
+//   warp 18, one lane: MMA issuer for both query tiles.  S = Q K^T (tcgen05.mma, both operands
 //                     K-major in shared memory) into tensor memory; O += P V with P read from tensor
-//                     memory (it overwrites the first half of S) and V, as stored (head dimension
+//                     memory (it lies over the scores it came from) and V, as stored (head dimension
 //                     contiguous), as an MN-major shared-memory operand.  The scores of a query
 //                     tile's next key tile are issued right after its P V, so one query tile's
-//                     softmax runs while the other's MMAs do.
-//   warps 0-3, 4-7:   softmax of query tile 0 and 1.  Each thread owns one query row.  Exponentials
-//                     are taken against the reference the row already has, without a maximum: the
-//                     reference only has to keep P and the sums in range, and the tile's sum tells
-//                     whether it did.  If it did not (or the row has no reference yet: the first
-//                     tile), the warp takes a second pass with the true maximum and rescales its
-//                     rows of O.  The sum uses the same reference, so the result is exact.  At the
-//                     end the thread divides its row of O by the sum and stores it.
+//                     softmax runs while the other's MMAs do.  An MMA of 128 x 128 x 16 keeps the
+//                     tensor pipe busy for 64 clocks and the pipe takes only a few MMAs ahead, while
+//                     a look at an mbarrier costs this thread 100 to 180 clocks even when the barrier
+//                     has long been passed (measured): so every barrier is looked at BEFORE the MMAs
+//                     of the group ahead of the one that needs it are issued, the answer is used
+//                     after them, and a key tile's keys and values share one barrier each way.
+//   warps 0-7, 8-15:  softmax of query tile 0 and 1.  Two threads own one query row: the warps of a
+//                     32-row quarter take the tile's keys 0-63 and 64-127 (a scheduler then has two
+//                     warps of a tile to switch between: one alone waits on latencies, not on the
+//                     special-function unit).  Exponentials are taken against the reference the row
+//                     already has, without a maximum: the reference only has to keep P and the sums in
+//                     range, and the tile's sum tells whether it did.  If it did not for either half
+//                     (or the row has no reference yet: the first tile), both warps take a second pass
+//                     with the row's true maximum and rescale their columns of O.  Each half keeps its
+//                     own sum against the common reference, so the result is exact.  The two warps
+//                     meet on an mbarrier of their own (votes, maxima and sums go through shared
+//                     memory).  Each half stores its P over its own scores: keys 0-63 in columns 0-31,
+//                     keys 64-127 in columns 64-95.  At the end each thread divides its half row of O
+//                     by the row's sum and stores it.
 // Tensor memory: 512 columns, per query tile 128 of scores / P and 128 of output.  Shared memory:
 // two query tiles, two key tiles, two value tiles of 32 KB.
 //
@@ -39,11 +50,13 @@ namespace fatc {
 using namespace tc;
 
 constexpr int kD = 128, kTileQ = 128, kTileK = 128, kPage = 64;
-constexpr int kWarpLoadK = 8, kWarpLoadV = 9, kWarpMma = 10;
-constexpr int kThreads = 352;
+constexpr int kWarpLoadK = 16, kWarpLoadV = 17, kWarpMma = 18;
+constexpr int kThreads = 608;
+constexpr int kHalfKeys = kTileK / 2;                  // keys of a tile that one softmax thread works on
 constexpr uint32_t kHalfTile = 128 * 128;              // bytes of [128 rows x 64 bfloat16]
 constexpr uint32_t kTileBytes = 2 * kHalfTile;         // [128 x 128] bfloat16
-// tensor memory columns of query tile b: kSubCols * b + ...; P overwrites the scores it came from
+// tensor memory columns of query tile b: kSubCols * b + ...; P overwrites the scores it came from: the P of
+// keys 64 h .. 64 h + 63 (32 columns of two bfloat16) lies at the start of those keys' own 64 score columns
 constexpr uint32_t kSubCols = 256, kColS = 0, kColP = 0, kColO = 128, kTmemCols = 512;
 
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -83,6 +96,13 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t* r) {
           "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
           "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
           "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
+// The same for 16 registers of tmem_ld16.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
         :: "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -136,7 +156,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Params p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t q_bar, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_done[2];
+    // kv_full[stage]: the keys and the values of a tile have landed (both producers arrive with their bytes);
+    // kv_empty[stage]: the MMAs on them have finished
+    __shared__ __align__(8) uint64_t q_bar, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_done[2];
+    __shared__ __align__(8) uint64_t pair_bar[2][4];         // the two softmax warps of (query tile, quarter) meet here
+    __shared__ float pair_value[2][2][kTileQ];               // [query tile][half][row]: this half's maximum, for the other half
+    __shared__ float pair_sum[2][2][kTileQ];                 // the same for the sums at the end (a thread that is done with its
+                                                             // last tile must not write over a maximum its partner has yet to read)
+    __shared__ int pair_vote[2][4][2];                       // [query tile][quarter][half]: this half wants the second pass
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
     volatile int* abort_flag = &abort_word;
@@ -152,11 +179,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         abort_word = 0;
         mbar_init(smem_u32(&q_bar), 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&k_full[i]), 1); mbar_init(smem_u32(&v_full[i]), 1);
-            mbar_init(smem_u32(&k_empty[i]), 1); mbar_init(smem_u32(&v_empty[i]), 1);
+            mbar_init(smem_u32(&kv_full[i]), 2);
+            mbar_init(smem_u32(&kv_empty[i]), 1);
             mbar_init(smem_u32(&s_full[i]), 1);
-            mbar_init(smem_u32(&p_full[i]), 4);
+            mbar_init(smem_u32(&p_full[i]), 8);
             mbar_init(smem_u32(&o_done[i]), 1);
+            for (int qd = 0; qd < 4; ++qd) mbar_init(smem_u32(&pair_bar[i][qd]), 2);
         }
         fence_barrier_init();
         fence_async_proxy();
@@ -218,8 +246,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const bool second = key0 + kPage <= last_key;
                 const int page_b = second ? pages[key0 / kPage + 1] : page_a;
                 const int ra = (page_a * p.nkv + g) * kPage, rb = (page_b * p.nkv + g) * kPage;
-                const uint32_t full = smem_u32(is_k ? &k_full[st] : &v_full[st]);
-                const uint32_t empty = smem_u32(is_k ? &k_empty[st] : &v_empty[st]);
+                const uint32_t full = smem_u32(&kv_full[st]), empty = smem_u32(&kv_empty[st]);
                 const uint32_t dst = (is_k ? s_k : s_v) + st * kTileBytes;
                 if (!mbar_wait(empty, ((i >> 1) & 1u) ^ 1u, abort_flag, p.error_flag, is_k ? 201 : 210)) break;
                 mbar_arrive_expect_tx(full, kTileBytes);
@@ -235,95 +262,134 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t idesc_qk = instr_desc_bf16(kTileQ, kTileK);
             constexpr uint32_t idesc_pv = instr_desc_bf16(kTileQ, kD) | (1u << 16);        // B is MN-major
             bool ok = true;
-            int k_ready = t_lo - 1, v_ready = t_lo - 1;       // key / value tiles whose arrival this thread has seen
-            // MMAs of one thread run in the order they are issued, so the scores of tile t+1, issued after
-            // P V of tile t, overwrite P only when that product has read it.
+            // Every descriptor is made once, before the loop; a K slice is an addition of a constant to its address
+            // field (16-byte units; the tiles are far below the field's 256 KB).
+            constexpr uint64_t kTileUnits = kTileBytes >> 4;     // the second tile of a pair, in the address field's units
+            const uint64_t dq0 = smem_desc_sw128(s_q, 0), dk0 = smem_desc_sw128(s_k, 0), dv0 = smem_desc_mn_sw128(s_v, kHalfTile);
+            // A barrier this thread will need: looked at once ahead of time (`seen`), waited for only if that look
+            // came too early.
+            auto look_kv = [&](int t) -> bool {
+                return mbar_try_wait(smem_u32(&kv_full[(t - t_lo) & 1]), ((t - t_lo) >> 1) & 1u);
+            };
+            auto need_kv = [&](int t, bool seen) -> bool {
+                if (!seen && !mbar_wait(smem_u32(&kv_full[(t - t_lo) & 1]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 203)) return false;
+                return true;
+            };
+            auto look_p = [&](int b, int t) -> bool {
+                return mbar_try_wait(smem_u32(&p_full[b]), (uint32_t)(t - qt[b].tile_lo) & 1u);
+            };
+            auto need_p = [&](int b, int t, bool seen) -> bool {
+                if (!seen && !mbar_wait(smem_u32(&p_full[b]), (uint32_t)(t - qt[b].tile_lo) & 1u, abort_flag, p.error_flag, 205)) return false;
+                tc_fence_after();
+                return true;
+            };
+            // MMAs of one thread run and finish in the order they are issued: the scores of tile t+1, issued after
+            // P V of tile t, overwrite P only when that product has read it, and their commit also says that P V of
+            // tile t has finished (the softmax threads rely on it when they rescale O).
             auto issue_qk = [&](int b, int t) {
-                const int st = (t - t_lo) & 1;
-                if (k_ready < t) {
-                    if (!mbar_wait(smem_u32(&k_full[st]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 203)) { ok = false; return; }
-                    tc_fence_after();
-                    k_ready = t;
-                }
-                const uint32_t q_tile = s_q + b * kTileBytes, k_tile = s_k + st * kTileBytes;
+                const uint64_t a0 = dq0 + (b ? kTileUnits : 0), b0 = dk0 + (((t - t_lo) & 1) ? kTileUnits : 0);
+                const uint32_t d = tmem + b * kSubCols + kColS;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t half = (ks >> 2) * kHalfTile, off = (ks & 3) * 32;
-                    mma_bf16(tmem + b * kSubCols + kColS, smem_desc_sw128(q_tile + half, off), smem_desc_sw128(k_tile + half, off),
-                             idesc_qk, ks > 0 ? 1u : 0u);
+                    constexpr uint32_t kHalfUnits = kHalfTile >> 4;
+                    const uint64_t step = (uint64_t)((ks >> 2) * kHalfUnits + (ks & 3) * 2);      // 64-element half, then 32 bytes a slice
+                    mma_bf16(d, a0 + step, b0 + step, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 mma_commit(smem_u32(&s_full[b]));
             };
-            ok = mbar_wait(smem_u32(&q_bar), 0, abort_flag, p.error_flag, 202);
+            auto issue_pv = [&](int b, int t) {
+                const uint64_t v0 = dv0 + (((t - t_lo) & 1) ? kTileUnits : 0);
+                const uint32_t d = tmem + b * kSubCols + kColO, pa = tmem + b * kSubCols + kColP;
+                const uint32_t first = t > qt[b].tile_lo ? 1u : 0u;
 #pragma unroll
-            for (int b = 0; b < 2; ++b)
-                if (ok && qt[b].reads(t_lo)) issue_qk(b, t_lo);
-            if (ok) mma_commit(smem_u32(&k_empty[0]));
+                for (int jj = 0; jj < kTileK / 16; ++jj)          // 16 keys: 16 rows of 128 bytes of V, 8 columns of P
+                    mma_bf16_ts(d, pa + (jj >> 2) * kHalfKeys + (jj & 3) * 8, v0 + (uint64_t)(jj * ((16 * 128) >> 4)), idesc_pv,
+                                jj > 0 ? 1u : first);
+                if (t == qt[b].tile_hi) mma_commit(smem_u32(&o_done[b]));
+            };
+            ok = mbar_wait(smem_u32(&q_bar), 0, abort_flag, p.error_flag, 202) && need_kv(t_lo, false);
+            if (ok) {
+                tc_fence_after();
+                if (qt[0].reads(t_lo)) issue_qk(0, t_lo);
+                if (qt[1].reads(t_lo)) issue_qk(1, t_lo);
+            }
+            // the order of a key tile's groups of MMAs: P V of query tile 0, its next scores, P V of query tile 1,
+            // its next scores; each look is placed one group ahead of the wait it may spare
+            bool seen_p0 = false;                             // P of query tile 0 for tile t
             for (int t = t_lo; t <= t_hi && ok; ++t) {
-                const int st = (t - t_lo) & 1;
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    if (!ok) break;
-                    if (qt[b].reads(t)) {
-                        const int j = t - qt[b].tile_lo;      // this query tile's own count of key tiles
-                        if (!mbar_wait(smem_u32(&p_full[b]), j & 1u, abort_flag, p.error_flag, 205)) { ok = false; break; }
-                        if (v_ready < t) {
-                            if (!mbar_wait(smem_u32(&v_full[st]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 206)) { ok = false; break; }
-                            v_ready = t;
-                        }
-                        tc_fence_after();
-                        const uint32_t v_tile = s_v + st * kTileBytes;
-#pragma unroll
-                        for (int jj = 0; jj < kTileK / 16; ++jj)
-                            mma_bf16_ts(tmem + b * kSubCols + kColO, tmem + b * kSubCols + kColP + jj * 8,
-                                        smem_desc_mn_sw128(v_tile + jj * 16 * 128, kHalfTile), idesc_pv, (j > 0 || jj > 0) ? 1u : 0u);
-                        mma_commit(smem_u32(&o_done[b]));
-                    }
-                    if (b == 1) mma_commit(smem_u32(&v_empty[st]));
-                    if (t + 1 <= t_hi && qt[b].reads(t + 1)) issue_qk(b, t + 1);
-                    if (b == 1 && t + 1 <= t_hi && ok) mma_commit(smem_u32(&k_empty[st ^ 1]));
+                const bool more = t + 1 <= t_hi;
+                const bool seen_kv = more && look_kv(t + 1);                 // for the scores of tile t + 1
+                if (qt[0].reads(t)) {
+                    if (!need_p(0, t, seen_p0)) { ok = false; break; }
+                    issue_pv(0, t);
                 }
+                const bool seen_p1 = qt[1].reads(t) && look_p(1, t);         // for P V of query tile 1
+                if (more) {
+                    if (!need_kv(t + 1, seen_kv)) { ok = false; break; }
+                    if (qt[0].reads(t + 1)) issue_qk(0, t + 1);
+                }
+                if (qt[1].reads(t)) {
+                    if (!need_p(1, t, seen_p1)) { ok = false; break; }
+                    issue_pv(1, t);
+                }
+                // the tile's keys and values are free when everything issued so far has finished
+                mma_commit(smem_u32(&kv_empty[(t - t_lo) & 1]));
+                seen_p0 = more && qt[0].reads(t + 1) && look_p(0, t + 1);    // most likely too early: then it is waited for
+                if (more && qt[1].reads(t + 1)) issue_qk(1, t + 1);
             }
         }
         __syncwarp();
     } else {
-        // softmax of query tile b: this thread owns its row `r`
-        const int b = warp >> 2, quarter = warp & 3;
+        // softmax of query tile b: this thread owns keys 64 half .. 64 half + 63 of its row `r`
+        const int b = warp >> 3, half = (warp >> 2) & 1, quarter = warp & 3;
         const QueryTile me = b ? qt[1] : qt[0];
         const int tiles = me.tile_hi - me.tile_lo + 1;        // 0 for a query tile without rows
         const int r = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t sub = tmem + b * kSubCols + lane_addr;
+        const uint32_t s_addr = sub + kColS + half * kHalfKeys;       // this thread's 64 scores; its P goes over their start
         const int pos = past + me.q0 + r;
         const int lo = p.window > 0 ? pos - p.window + 1 : 0;
         const int warp_pos = past + me.q0 + quarter * 32;
-        float m_ref = -INFINITY, l = 0.0f;                    // reference maximum (raw score units) and sum
+        const uint32_t meet = smem_u32(&pair_bar[b][quarter]);
+        uint32_t meetings = 0;
+        float m_ref = -INFINITY, l = 0.0f;                    // the row's reference maximum (raw score units), this half's sum
         bool ok = true;
+        // Both warps of the pair arrive and wait; what either wrote to shared memory before is visible to both after.
+        auto meet_partner = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(meet);
+            const bool met = mbar_wait(meet, meetings & 1u, abort_flag, p.error_flag, 211);
+            ++meetings;
+            return met;
+        };
         for (int t = 0; t < tiles && ok; ++t) {
-            const int key0 = (me.tile_lo + t) * kTileK;
-            const uint32_t s_addr = sub + kColS;
+            const int key0 = (me.tile_lo + t) * kTileK + half * kHalfKeys;
             if (!mbar_wait(smem_u32(&s_full[b]), t & 1u, abort_flag, p.error_flag, 207)) { ok = false; break; }
             tc_fence_after();
-            const bool masked = key0 + kTileK - 1 > warp_pos || (p.window > 0 && key0 < warp_pos + 31 - p.window + 1);
-            uint32_t pk[64];                                  // P of this row, two bfloat16 a register
+            const bool masked = key0 + kHalfKeys - 1 > warp_pos || (p.window > 0 && key0 < warp_pos + 31 - p.window + 1);
+            uint32_t pk[32];                                  // P of this half row, two bfloat16 a register
+            uint32_t a[16], bb[16];
+            auto mask16 = [&](uint32_t (&h)[16], int c_base) {
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int key = key0 + c_base + c;
+                        if (key > pos || key < lo) h[c] = 0xff800000u;                    // -inf
+                    }
+                }
+            };
             bool two_pass = t == 0;
             if (!two_pass) {
-                // One pass, 32 scores at a time while the next 32 are on their way from tensor memory.  A P above
+                // One pass, 16 scores at a time while the next 16 are on their way from tensor memory.  A P above
                 // 2^15 makes the sum exceed 2^15, and a sum above 2^15 needs a P above 2^8: past that the
                 // reference is renewed.  The scores stay in tensor memory until P is stored over them.
                 const float ref = m_ref == -INFINITY ? 0.0f : m_ref * p.scale_log2;
                 float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-                uint32_t a[32], bb[32];
-                auto chunk = [&](uint32_t* h, int c_base, uint32_t* dst) {
-                    if (masked) {
+                auto chunk = [&](uint32_t (&h)[16], int c_base) {
+                    mask16(h, c_base);
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const int key = key0 + c_base + c;
-                            if (key > pos || key < lo) h[c] = 0xff800000u;            // -inf
-                        }
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
+                    for (int c = 0; c < 16; c += 8) {
                         float e[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) e[i] = ex2(fmaf(__uint_as_float(h[c + i]), p.scale_log2, -ref));
@@ -331,53 +397,47 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                         for (int i = 0; i < 8; i += 2) {
                             __nv_bfloat162 h2 = __floats2bfloat162_rn(e[i], e[i + 1]);
-                            dst[(c + i) >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+                            pk[(c_base + c + i) >> 1] = *reinterpret_cast<uint32_t*>(&h2);
                         }
                     }
                 };
-                tmem_ld32(s_addr, a);
-                tmem_ld_wait32(a);
-                tmem_ld32(s_addr + 32, bb);
-                chunk(a, 0, pk);
-                tmem_ld_wait32(bb);
-                tmem_ld32(s_addr + 64, a);
-                chunk(bb, 32, pk + 16);
-                tmem_ld_wait32(a);
-                tmem_ld32(s_addr + 96, bb);
-                chunk(a, 64, pk + 32);
-                tmem_ld_wait32(bb);
-                chunk(bb, 96, pk + 48);
+                tmem_ld16(s_addr, a);
+                tmem_ld_wait16(a);
+                tmem_ld16(s_addr + 16, bb);
+                chunk(a, 0);
+                tmem_ld_wait16(bb);
+                tmem_ld16(s_addr + 32, a);
+                chunk(bb, 16);
+                tmem_ld_wait16(a);
+                tmem_ld16(s_addr + 48, bb);
+                chunk(a, 32);
+                tmem_ld_wait16(bb);
+                chunk(bb, 48);
                 const float tile_sum = (s0 + s1) + (s2 + s3);
                 const bool in_range = tile_sum <= 32768.0f && m_ref != -INFINITY;      // false for inf and NaN too
-                two_pass = __any_sync(0xffffffffu, !in_range);
+                const bool mine = __any_sync(0xffffffffu, !in_range);
+                if (lane == 0) pair_vote[b][quarter][half] = mine ? 1 : 0;
+                if (!meet_partner()) { ok = false; break; }
+                two_pass = mine || pair_vote[b][quarter][half ^ 1] != 0;
                 if (!two_pass) l += tile_sum;
             }
             if (two_pass) {
-                // The row's maximum first, 64 scores at a time (the first half is dropped and read again),
-                // then the exponentials against a reference that grows only when the maximum has run away
-                // from it by more than 2^8.
-                uint32_t h[64];
-                auto load_half = [&](int c_base) {
-                    tmem_ld32(s_addr + c_base, h);
-                    tmem_ld32(s_addr + c_base + 32, h + 32);
-                    tmem_ld_wait32(h);
-                    tmem_ld_wait32(h + 32);
-                    if (masked) {
-#pragma unroll
-                        for (int c = 0; c < 64; ++c) {
-                            const int key = key0 + c_base + c;
-                            if (key > pos || key < lo) h[c] = 0xff800000u;            // -inf
-                        }
-                    }
-                };
+                // The row's maximum first (this half's, then the other's through shared memory), then the exponentials
+                // against a reference that grows only when the maximum has run away from it by more than 2^8.
                 float mx0 = -INFINITY, mx1 = -INFINITY;
-                load_half(0);
+#pragma unroll 1
+                for (int c_base = 0; c_base < kHalfKeys; c_base += 16) {
+                    tmem_ld16(s_addr + c_base, a);
+                    tmem_ld_wait16(a);
+                    mask16(a, c_base);
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) { mx0 = fmaxf(mx0, __uint_as_float(h[c])); mx1 = fmaxf(mx1, __uint_as_float(h[c + 1])); }
-                load_half(64);
-#pragma unroll
-                for (int c = 0; c < 64; c += 2) { mx0 = fmaxf(mx0, __uint_as_float(h[c])); mx1 = fmaxf(mx1, __uint_as_float(h[c + 1])); }
-                const float mx = fmaxf(mx0, mx1);
+                    for (int c = 0; c < 16; c += 2) { mx0 = fmaxf(mx0, __uint_as_float(a[c])); mx1 = fmaxf(mx1, __uint_as_float(a[c + 1])); }
+                }
+                pair_value[b][half][r] = fmaxf(mx0, mx1);
+                if (!meet_partner()) { ok = false; break; }
+                const float mx = fmaxf(fmaxf(mx0, mx1), pair_value[b][half ^ 1][r]);
+                // (this slot is written again only after the partner has read it: the next tile's scores, which both wait
+                // for, are issued after the partner's arrival on p_full, which follows its read)
                 float alpha = 1.0f;
                 const bool grow = (mx - m_ref) * p.scale_log2 > 8.0f || m_ref == -INFINITY;
                 if (grow && mx > -INFINITY) {
@@ -388,59 +448,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const bool rescale = t > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
                 const float ref = m_ref == -INFINITY ? 0.0f : m_ref * p.scale_log2;
                 float sum0 = 0.0f, sum1 = 0.0f;
-                auto exp_pack = [&](uint32_t* dst) {              // 64 scores -> 32 registers of two bfloat16
+#pragma unroll 1
+                for (int c_base = 0; c_base < kHalfKeys; c_base += 16) {
+                    tmem_ld16(s_addr + c_base, a);
+                    tmem_ld_wait16(a);
+                    mask16(a, c_base);
 #pragma unroll
-                    for (int c = 0; c < 64; c += 4) {
-                        const float e0 = ex2(fmaf(__uint_as_float(h[c]), p.scale_log2, -ref));
-                        const float e1 = ex2(fmaf(__uint_as_float(h[c + 1]), p.scale_log2, -ref));
-                        const float e2 = ex2(fmaf(__uint_as_float(h[c + 2]), p.scale_log2, -ref));
-                        const float e3 = ex2(fmaf(__uint_as_float(h[c + 3]), p.scale_log2, -ref));
+                    for (int c = 0; c < 16; c += 4) {
+                        const float e0 = ex2(fmaf(__uint_as_float(a[c]), p.scale_log2, -ref));
+                        const float e1 = ex2(fmaf(__uint_as_float(a[c + 1]), p.scale_log2, -ref));
+                        const float e2 = ex2(fmaf(__uint_as_float(a[c + 2]), p.scale_log2, -ref));
+                        const float e3 = ex2(fmaf(__uint_as_float(a[c + 3]), p.scale_log2, -ref));
                         sum0 += e0 + e1; sum1 += e2 + e3;
                         __nv_bfloat162 h01 = __floats2bfloat162_rn(e0, e1), h23 = __floats2bfloat162_rn(e2, e3);
-                        dst[c >> 1] = *reinterpret_cast<uint32_t*>(&h01);
-                        dst[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h23);
+                        // a loop that is not unrolled cannot index registers: the chunk's P goes to tensor memory at the end
+                        bb[c >> 1] = *reinterpret_cast<uint32_t*>(&h01);
+                        bb[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h23);
                     }
-                };
-                exp_pack(pk + 32);
-                load_half(0);
-                exp_pack(pk);
-                l += sum0 + sum1;
-                // O must be quiet before it is rescaled (P V of the tile before has ended by then anyway: the
-                // scores of this tile were issued after it)
-                if (rescale) {
-                    if (!mbar_wait(smem_u32(&o_done[b]), (t - 1) & 1u, abort_flag, p.error_flag, 208)) { ok = false; break; }
-                    tc_fence_after();
-#pragma unroll 1
-                    for (int c0 = 0; c0 < kD; c0 += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(sub + kColO + c0, v);
-                        tmem_ld_wait32(v);
+                    // this chunk's P (8 registers) over the start of the scores already read: chunk i's P lies in
+                    // columns 8 i .. 8 i + 7, behind the 16 i .. 16 i + 15 its scores came from and never ahead of a
+                    // chunk still to be read
+                    uint32_t w8[8];
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-                        tmem_st32(sub + kColO + c0, v);
+                    for (int i = 0; i < 8; ++i) w8[i] = bb[i];
+                    tmem_st8(s_addr + (c_base >> 1), w8);
+                }
+                l += sum0 + sum1;
+                // O is quiet when it is rescaled: this tile's scores were issued after P V of the tile before by the same
+                // thread, MMAs finish in order, and the scores' arrival was waited for above
+                if (rescale) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kHalfKeys; c0 += 16) {
+                        tmem_ld16(sub + kColO + half * kHalfKeys + c0, a);
+                        tmem_ld_wait16(a);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
+                        tmem_st16(sub + kColO + half * kHalfKeys + c0, a);
                     }
                 }
+            } else {
+                tmem_st32(s_addr, pk);
             }
-            tmem_st32(sub + kColP, pk);
-            tmem_st32(sub + kColP + 32, pk + 32);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[b]));
         }
-        if (ok && tiles > 0 && mbar_wait(smem_u32(&o_done[b]), (tiles - 1) & 1u, abort_flag, p.error_flag, 209)) {
+        // the row's sum is the two halves' sums; each thread normalises and stores its 64 columns of O
+        if (ok && tiles > 0) {
+            pair_sum[b][half][r] = l;
+            ok = meet_partner();
+            l += pair_sum[b][half ^ 1][r];
+        }
+        if (ok && tiles > 0 && mbar_wait(smem_u32(&o_done[b]), 0, abort_flag, p.error_flag, 209)) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const bool store = me.q0 + r < n_new;
-            __nv_bfloat16* dst = p.out + (size_t)(row0 + me.q0 + r) * p.out_stride + (size_t)me.head * kD;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + me.q0 + r) * p.out_stride + (size_t)me.head * kD + half * kHalfKeys;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kD; c0 += 32) {
-                uint32_t ov[32];
-                tmem_ld32(sub + kColO + c0, ov);
-                tmem_ld_wait32(ov);
+            for (int c0 = 0; c0 < kHalfKeys; c0 += 16) {
+                uint32_t ov[16];
+                tmem_ld16(sub + kColO + half * kHalfKeys + c0, ov);
+                tmem_ld_wait16(ov);
                 if (store) {
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
+                    for (int c = 0; c < 16; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
