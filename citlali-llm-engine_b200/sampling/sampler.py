@@ -24,7 +24,7 @@ class Sampler:
     def _grow(self, rows: int):
         self.max_rows = rows
         pin = self.device.type == "cuda"
-        self._params_host = torch.zeros((2, rows), dtype=torch.float32, pin_memory=pin)
+        self._pin = pin
         self._params = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
         self._tokens = torch.zeros(rows, dtype=torch.int32, device=self.device)
         self._tokens_host = torch.zeros(rows, dtype=torch.int32, pin_memory=pin)
@@ -39,9 +39,13 @@ class Sampler:
             ops.argmax_rows(logits, tokens)
             return tokens
         require(len(uniforms) == rows, "one uniform number per sampled row is needed")
-        self._params_host[0, :rows] = float(temperature)
-        self._params_host[1, :rows] = torch.as_tensor(list(uniforms), dtype=torch.float32)
-        self._params.copy_(self._params_host, non_blocking=True)
+        # a pinned buffer of its own for every call: the caller need not wait for this copy before it samples again
+        host = torch.empty((2, rows), dtype=torch.float32)
+        host[0] = float(temperature)
+        host[1] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+        if self._pin:
+            host = host.pin_memory()
+        self._params[:, :rows].copy_(host, non_blocking=True)
         ops.sample_rows(logits, self._params[0], self._params[1], tokens)
         return tokens
 
