@@ -129,7 +129,9 @@ def run_workload(index, repetitions):
             runs.append(dict(session.stats))
         print(f"[bench] {w['name']} run {rep}: {session.stats}", file=sys.stderr, flush=True)
     clock_record = clocks.stop()
-    run = sorted(runs, key=lambda r: r["decode_s"])[len(runs) // 2]
+    # the median of each figure on its own (a run with the median decode time may hold a prompt step that a
+    # page fault or an allocation disturbed)
+    run = {k: statistics.median(r[k] for r in runs) for k in runs[0]}
     H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
     nq, nkv, layers = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.num_hidden_layers
     layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I

@@ -42,7 +42,14 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream's handle.  Asked for at every launch, so by the quick route where torch has one
+    (a step launches a few hundred kernels and the host must not be what a short prompt waits for)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -68,9 +75,9 @@ def _check(code: int, what: str):
 
 def _need_cuda(*tensors):
     for t in tensors:
-        if t is not None:
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
             require(t.is_cuda, "kernels run on a CUDA device only; a tensor on the CPU was given")
-            require(t.is_contiguous(), "kernels take contiguous tensors")
+            require(False, "kernels take contiguous tensors")
 
 
 _i = ctypes.c_int
@@ -273,10 +280,11 @@ _workspace = {}
 
 
 def sm_count(device) -> int:
-    idx = torch.device(device).index or 0
-    if idx not in _sm_count:
-        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
-    return _sm_count[idx]
+    idx = (device.index if isinstance(device, torch.device) else torch.device(device).index) or 0
+    n = _sm_count.get(idx)
+    if n is None:
+        n = _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def gemm_tc_plan(M: int, N: int, K: int, device, force_splits: int = 0) -> dict:
