@@ -116,6 +116,80 @@ __device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// A look at an mbarrier costs the issuing thread 100 to 180 clocks during which it issues nothing, and the tensor
+// pipe, which takes only a few MMAs ahead, runs dry.  In these two the look (`mbarrier.try_wait`, one try) is
+// issued FIRST and its answer is taken LAST, with a group's eight MMAs between them in one statement, so that the
+// MMAs go out while the look is on its way.  Returns whether phase `parity` of `bar` had completed.
+//
+// S[128 x 128] = A . B^T over the head size 128: eight K slices; an operand's two 64-element halves lie
+// `half_units` (in 16-byte units) apart, a slice within a half 32 bytes (2 units) after the one before.
+__device__ __forceinline__ bool mma_scores_and_look(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                    uint32_t bar, uint32_t parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n"
+        ".reg .pred look, yes, no;\n"
+        ".reg .b64 a, b;\n"
+        "setp.eq.u32 yes, 0, 0;\n"
+        "setp.ne.u32 no, 0, 0;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 look, [%5], %6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, no;\n"
+        "add.u64 a, %2, 2;\n add.u64 b, %3, 2;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 4;\n add.u64 b, %3, 4;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 6;\n add.u64 b, %3, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 1024;\n add.u64 b, %3, 1024;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 1026;\n add.u64 b, %3, 1026;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 1028;\n add.u64 b, %3, 1028;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "add.u64 a, %2, 1030;\n add.u64 b, %3, 1030;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], a, b, %4, yes;\n"
+        "selp.b32 %0, 1, 0, look;\n"
+        "}"
+        : "=r"(seen) : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(bar), "r"(parity) : "memory");
+    return seen != 0;
+}
+// O[128 x 128] (+)= P . V over a tile's 128 keys: eight slices of 16 keys; P's slice j lies at tensor-memory column
+// (j / 4) * 64 + (j % 4) * 8 of `tmem_p` (each half of the keys has its P at the start of its own scores), V's
+// slice is 16 rows of 128 bytes (128 units) after the one before.  `accumulate` = 0 starts O anew.
+__device__ __forceinline__ bool mma_values_and_look(uint32_t tmem_d, uint32_t tmem_p, uint64_t desc_v, uint32_t idesc,
+                                                    uint32_t accumulate, uint32_t bar, uint32_t parity) {
+    uint32_t seen;
+    asm volatile(
+        "{\n"
+        ".reg .pred look, yes, first;\n"
+        ".reg .b64 v;\n"
+        ".reg .b32 pp;\n"
+        "setp.eq.u32 yes, 0, 0;\n"
+        "setp.ne.b32 first, %5, 0;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 look, [%6], %7;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, first;\n"
+        "add.u32 pp, %2, 8;\n add.u64 v, %3, 128;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 16;\n add.u64 v, %3, 256;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 24;\n add.u64 v, %3, 384;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 64;\n add.u64 v, %3, 512;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 72;\n add.u64 v, %3, 640;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 80;\n add.u64 v, %3, 768;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "add.u32 pp, %2, 88;\n add.u64 v, %3, 896;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], [pp], v, %4, yes;\n"
+        "selp.b32 %0, 1, 0, look;\n"
+        "}"
+        : "=r"(seen) : "r"(tmem_d), "r"(tmem_p), "l"(desc_v), "r"(idesc), "r"(accumulate), "r"(bar), "r"(parity) : "memory");
+    return seen != 0;
+}
+static_assert(kHalfTile >> 4 == 1024 && kHalfKeys == 64 && kD == 128 && kTileK == 128,
+              "the offsets written into mma_scores_and_look and mma_values_and_look are those of 128 x 128 tiles");
+
 // Shared-memory descriptor of an MN-major operand with 128-byte swizzle: rows of 128 bytes hold 64
 // consecutive elements of the MN dimension, consecutive rows are consecutive K indices, groups of 8
 // rows are 1024 bytes apart, and the next 64 MN elements start `mn_step` bytes further.
@@ -275,9 +349,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!seen && !mbar_wait(smem_u32(&kv_full[(t - t_lo) & 1]), ((t - t_lo) >> 1) & 1u, abort_flag, p.error_flag, 203)) return false;
                 return true;
             };
-            auto look_p = [&](int b, int t) -> bool {
-                return mbar_try_wait(smem_u32(&p_full[b]), (uint32_t)(t - qt[b].tile_lo) & 1u);
-            };
             auto need_p = [&](int b, int t, bool seen) -> bool {
                 if (!seen && !mbar_wait(smem_u32(&p_full[b]), (uint32_t)(t - qt[b].tile_lo) & 1u, abort_flag, p.error_flag, 205)) return false;
                 tc_fence_after();
@@ -286,56 +357,64 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // MMAs of one thread run and finish in the order they are issued: the scores of tile t+1, issued after
             // P V of tile t, overwrite P only when that product has read it, and their commit also says that P V of
             // tile t has finished (the softmax threads rely on it when they rescale O).
-            auto issue_qk = [&](int b, int t) {
+            // Each group of eight MMAs carries a look at the barrier that the NEXT group will need (see
+            // mma_scores_and_look); `look_bar` 0 means there is nothing to look at (the Q barrier, long passed, stands in).
+            const uint32_t passed_bar = smem_u32(&q_bar);
+            auto issue_qk = [&](int b, int t, uint32_t look_bar, uint32_t look_parity) -> bool {
                 const uint64_t a0 = dq0 + (b ? kTileUnits : 0), b0 = dk0 + (((t - t_lo) & 1) ? kTileUnits : 0);
-                const uint32_t d = tmem + b * kSubCols + kColS;
-#pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    constexpr uint32_t kHalfUnits = kHalfTile >> 4;
-                    const uint64_t step = (uint64_t)((ks >> 2) * kHalfUnits + (ks & 3) * 2);      // 64-element half, then 32 bytes a slice
-                    mma_bf16(d, a0 + step, b0 + step, idesc_qk, ks > 0 ? 1u : 0u);
-                }
+                const bool seen = mma_scores_and_look(tmem + b * kSubCols + kColS, a0, b0, idesc_qk,
+                                                      look_bar ? look_bar : passed_bar, look_bar ? look_parity : 0u);
                 mma_commit(smem_u32(&s_full[b]));
+                return seen && look_bar != 0;
             };
-            auto issue_pv = [&](int b, int t) {
+            auto issue_pv = [&](int b, int t, uint32_t look_bar, uint32_t look_parity) -> bool {
                 const uint64_t v0 = dv0 + (((t - t_lo) & 1) ? kTileUnits : 0);
-                const uint32_t d = tmem + b * kSubCols + kColO, pa = tmem + b * kSubCols + kColP;
-                const uint32_t first = t > qt[b].tile_lo ? 1u : 0u;
-#pragma unroll
-                for (int jj = 0; jj < kTileK / 16; ++jj)          // 16 keys: 16 rows of 128 bytes of V, 8 columns of P
-                    mma_bf16_ts(d, pa + (jj >> 2) * kHalfKeys + (jj & 3) * 8, v0 + (uint64_t)(jj * ((16 * 128) >> 4)), idesc_pv,
-                                jj > 0 ? 1u : first);
+                const bool seen = mma_values_and_look(tmem + b * kSubCols + kColO, tmem + b * kSubCols + kColP, v0, idesc_pv,
+                                                      t > qt[b].tile_lo ? 1u : 0u, look_bar ? look_bar : passed_bar,
+                                                      look_bar ? look_parity : 0u);
                 if (t == qt[b].tile_hi) mma_commit(smem_u32(&o_done[b]));
+                return seen && look_bar != 0;
             };
+            auto kv_bar = [&](int t) -> uint32_t { return smem_u32(&kv_full[(t - t_lo) & 1]); };
+            auto kv_parity = [&](int t) -> uint32_t { return ((t - t_lo) >> 1) & 1u; };
+            auto p_parity = [&](int b, int t) -> uint32_t { return (uint32_t)(t - qt[b].tile_lo) & 1u; };
             ok = mbar_wait(smem_u32(&q_bar), 0, abort_flag, p.error_flag, 202) && need_kv(t_lo, false);
             if (ok) {
                 tc_fence_after();
-                if (qt[0].reads(t_lo)) issue_qk(0, t_lo);
-                if (qt[1].reads(t_lo)) issue_qk(1, t_lo);
+                if (qt[0].reads(t_lo)) issue_qk(0, t_lo, 0, 0);
+                if (qt[1].reads(t_lo)) issue_qk(1, t_lo, 0, 0);
             }
-            // the order of a key tile's groups of MMAs: P V of query tile 0, its next scores, P V of query tile 1,
-            // its next scores; each look is placed one group ahead of the wait it may spare
+            // the order of a key tile's groups of MMAs: P V of query tile 0 (looking at the next tile's keys and
+            // values), its next scores (looking at P of query tile 1), P V of query tile 1, the next scores of query
+            // tile 1 (looking at the next P of query tile 0, most likely too early: then it is waited for)
             bool seen_p0 = false;                             // P of query tile 0 for tile t
             for (int t = t_lo; t <= t_hi && ok; ++t) {
                 const bool more = t + 1 <= t_hi;
-                const bool seen_kv = more && look_kv(t + 1);                 // for the scores of tile t + 1
+                bool seen_kv = false, seen_p1 = false;
                 if (qt[0].reads(t)) {
                     if (!need_p(0, t, seen_p0)) { ok = false; break; }
-                    issue_pv(0, t);
+                    seen_kv = issue_pv(0, t, more ? kv_bar(t + 1) : 0u, more ? kv_parity(t + 1) : 0u);
+                } else if (more) {
+                    seen_kv = look_kv(t + 1);
                 }
-                const bool seen_p1 = qt[1].reads(t) && look_p(1, t);         // for P V of query tile 1
                 if (more) {
                     if (!need_kv(t + 1, seen_kv)) { ok = false; break; }
-                    if (qt[0].reads(t + 1)) issue_qk(0, t + 1);
+                    if (qt[0].reads(t + 1)) {
+                        tc_fence_after();
+                        seen_p1 = issue_qk(0, t + 1, qt[1].reads(t) ? smem_u32(&p_full[1]) : 0u, qt[1].reads(t) ? p_parity(1, t) : 0u);
+                    }
                 }
                 if (qt[1].reads(t)) {
                     if (!need_p(1, t, seen_p1)) { ok = false; break; }
-                    issue_pv(1, t);
+                    issue_pv(1, t, 0, 0);
                 }
                 // the tile's keys and values are free when everything issued so far has finished
                 mma_commit(smem_u32(&kv_empty[(t - t_lo) & 1]));
-                seen_p0 = more && qt[0].reads(t + 1) && look_p(0, t + 1);    // most likely too early: then it is waited for
-                if (more && qt[1].reads(t + 1)) issue_qk(1, t + 1);
+                seen_p0 = false;
+                if (more && qt[1].reads(t + 1)) {
+                    const bool look = qt[0].reads(t + 1);
+                    seen_p0 = issue_qk(1, t + 1, look ? smem_u32(&p_full[0]) : 0u, look ? p_parity(0, t + 1) : 0u);
+                }
             }
         }
         __syncwarp();
