@@ -19,6 +19,10 @@ void citlali_set_dependent_launch(int enabled);
 int citlali_embed_rows(const void* table, int table_dtype, const int32_t* tokens, float* out,
                        int rows, int hidden, int vocab, float scale, int32_t* error_flag, cudaStream_t stream);
 
+// rows_out = bfloat16(x) [rows, hidden] and sumsq[r, g] = sum of x[r, 32 g .. 32 g + 31]^2 (hidden a multiple of 32):
+// what citlali_gemm_tc_normed's `scale_sumsq` reads, for rows that did not come out of an emitting product.
+int citlali_norm_inputs(const float* x, void* rows_out, float* sumsq, int rows, int hidden, cudaStream_t stream);
+
 // x[0..n) *= scale.
 int citlali_scale(float* x, size_t n, float scale, cudaStream_t stream);
 
@@ -113,6 +117,12 @@ int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force_splits, in
 // error_flag[1..2] receive the code and block of a wait that ran out.
 int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                     int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream);
+// The same for few rows of x with a layer norm's work in the epilogue (gemm_tcgen05.cu says what each pointer means;
+// null pointers: plain citlali_gemm_tc).
+int citlali_gemm_tc_normed(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                           int mode, int force_splits, int32_t* error_flag, int sm_count,
+                           void* emit_rows, float* emit_sumsq, const float* scale_sumsq, int scale_groups,
+                           int scale_dim, float scale_eps, cudaStream_t stream);
 // The same product on pairs of SMs (tcgen05.mma with cta_group::2: a [256 x BN] tile per cluster of two
 // blocks, each fetching half of both operands).  With equal waves it takes 0.92-0.97 of the one-block
 // kernel's time at 512 to 4,096 rows and 0.82 at 8,192, and it loses where its 256-row tiles need a wave

@@ -37,6 +37,23 @@ __global__ void embed_rows_kernel(const TW* __restrict__ table, const int32_t* _
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ldf(src, i) * scale : 0.0f;
 }
 
+// What a layer norm that lives in the products around it needs of rows it has not seen come out of a product: the rows
+// as bfloat16 and the sums of their squares over each 32 consecutive features (see citlali_gemm_tc_normed).  One block a
+// row, one warp a group of 32 features at a time.
+__global__ void norm_inputs_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ rows_out,
+                                   float* __restrict__ sumsq, int hidden) {
+    dependents_may_launch();
+    wait_for_predecessor();
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int groups = hidden >> 5;
+    for (int g = warp; g < groups; g += warps) {
+        const float v = x[(size_t)row * hidden + g * 32 + lane];
+        rows_out[(size_t)row * hidden + g * 32 + lane] = __float2bfloat16_rn(v);
+        const float sq = warp_sum(v * v);
+        if (lane == 0) sumsq[(size_t)row * groups + g] = sq;
+    }
+}
+
 // x *= scale over n floats (a logit scale; the reference has none).
 __global__ void scale_kernel(float* __restrict__ x, size_t n, float scale) {
     dependents_may_launch();
@@ -155,6 +172,16 @@ extern "C" int citlali_embed_rows(const void* table, int table_dtype, const int3
         launch_kernel(embed_rows_kernel<TW>, rows, 256, 0, stream, (const TW*)table, tokens, out, hidden, vocab, scale, error_flag);
         return CITLALI_LAUNCH_CHECK();
     });
+}
+
+extern "C" int citlali_norm_inputs(const float* x, void* rows_out, float* sumsq, int rows, int hidden, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden % 32 != 0) {
+        set_last_error("norm_inputs: the width %d must be a multiple of 32", hidden);
+        return kBadShape;
+    }
+    launch_kernel(norm_inputs_kernel, rows, hidden >= 2048 ? 512 : 128, 0, stream, x, (__nv_bfloat16*)rows_out, sumsq, hidden);
+    return CITLALI_LAUNCH_CHECK();
 }
 
 extern "C" int citlali_scale(float* x, size_t n, float scale, cudaStream_t stream) {

@@ -52,6 +52,17 @@ struct GemmParams {
     int rows_a, rows_b;    // rows of the 128-row operand and of the BN-row operand
     int splits;            // K is cut into this many ranges of whole 64-blocks
     int32_t* error_flag;
+    // Few rows of x only (the swapped form), for a layer norm that lives in the products around it instead of in a
+    // kernel of its own.  A product that adds into the float32 residual rows (kAddF32) may also EMIT what the norm of the
+    // updated rows needs: the rows as bfloat16 and the sums of their squares over each 32 consecutive features.  The
+    // product that follows reads those rows as its x and SCALES its result rows by rsqrt(sum of squares / dim + eps)
+    // (its weights carry the norm's gain): y = (x . (g * w)^T) * inv_rms(x) = (x * inv_rms(x) * g) . w^T.
+    __nv_bfloat16* emit_rows;      // [M, N] or null
+    float* emit_sumsq;             // [M, N / 32] (N a multiple of 32)
+    const float* scale_sumsq;      // [M, scale_groups] or null: sums of squares of the rows of this product's x
+    int scale_groups;
+    int scale_dim;
+    float scale_eps;
 };
 
 template <int BN>
@@ -88,7 +99,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full_bar[kAccStages], acc_empty_bar[kAccStages];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_word;
+    __shared__ float row_scale[kSwapped ? BN : 1];            // see GemmParams::scale_sumsq
     volatile int* abort_flag = &abort_word;
+    // An emitting product with a split K: the old residual values of the one unit this warp will own, fetched while the
+    // K loop runs (they have been final since the kernel ahead ended; fetched after the sums they would be a load from
+    // memory at the very end of the kernel, which costs more than the norm kernel this saves)
+    float x_old[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    bool have_old = false;
 
     dependents_may_launch();
     const uint32_t raw = smem_u32(smem_raw);
@@ -238,6 +255,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint64_t out_policy = l2_evict_first_policy();
         wait_for_predecessor();      // the epilogue reads and writes memory other kernels use
 
+        // The factor of every row of x, if this product scales its rows: a warp adds a row's partial sums of squares in
+        // an order that depends on their number alone.  (The swapped form has one tile of x: rows 0 .. M - 1.)
+        bool scaled = false;
+        if constexpr (kSwapped) {
+            scaled = p.scale_sumsq != nullptr;
+            if (scaled) {
+                constexpr int kWarps = epilogue_warps(kSwapped, BN);
+                for (int m = warp - 2; m < p.M && m < BN; m += kWarps) {
+                    float sum = 0.0f;
+                    for (int g0 = lane; g0 < p.scale_groups; g0 += 32) sum += p.scale_sumsq[(size_t)m * p.scale_groups + g0];
+                    sum = warp_sum(sum);
+                    if (lane == 0) row_scale[m] = rsqrtf(sum / (float)p.scale_dim + p.scale_eps);
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * kWarps) : "memory");      // the epilogue warps only
+            }
+        }
+        const bool emits = kSwapped && p.out_kind == kAddF32 && p.emit_rows != nullptr;
+        const int emit_groups = p.N >> 5;
+        if (kSwapped && emits && p.splits > 1) {
+            int ta, tb, sp;
+            decode(blockIdx.x, ta, tb, sp);                   // a split tile is its block's only unit of work
+            const int unit = (warp - 2) * p.splits + sp;      // the first (mostly the only) unit of the tile this warp owns
+            if (warp - 2 < (BN + p.splits - 1) / p.splits && unit < BN) {
+                const int m0 = tb * BN + (unit >> 2) * 4, n = ta * kBM + (unit & 3) * 32 + lane;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (n < p.N && m0 + e < p.M) x_old[e] = ((const float*)p.out)[(size_t)(m0 + e) * p.N + n];
+                have_old = true;
+            }
+        }
+
         // What becomes of 16 finished values: row i of the 128-row operand, rows j0 .. j0+15 of the other.
         auto finish = [&](const float (&v)[16], int i, int j0, int c0) {
             if constexpr (!kSwapped) {
@@ -250,10 +298,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int o_col = (i >> 5) * 16 + (lane & 15);
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[c], 16);
                     const int m = j0 + c;
+                    const float mine = scaled && m < p.M ? v[c] * row_scale[m] : v[c];
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
                     if ((lane & 16) == 0 && i < p.N && m < p.M)
-                        outh[(size_t)m * half_n + o_col] = __float2bfloat16_rn(silu_mul(v[c], other));
+                        outh[(size_t)m * half_n + o_col] = __float2bfloat16_rn(silu_mul(mine, other));
+                }
+            } else if (emits) {
+                // x[m, n] += v, and the updated row goes out as bfloat16 with the sum of its squares over this warp's
+                // 32 features (every lane takes part in the sum; a lane past the matrix adds nothing)
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int m = j0 + c;
+                    float sq = 0.0f;
+                    if (i < p.N && m < p.M) {
+                        const size_t o = (size_t)m * p.N + i;
+                        const float xn = outf[o] + v[c];
+                        outf[o] = xn;
+                        p.emit_rows[o] = __float2bfloat16_rn(xn);
+                        sq = xn * xn;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0 && i < p.N && m < p.M) p.emit_sumsq[(size_t)m * emit_groups + (i >> 5)] = sq;
                 }
             } else if (i < p.N) {
                 // out[m, n]; lanes hold consecutive n
@@ -262,9 +328,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int m = j0 + c;
                     if (m < p.M) {
                         const size_t o = (size_t)m * p.N + i;
-                        if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[c]);
-                        else if (p.out_kind == kAddF32) red_add_f32(outf + o, v[c]);
-                        else outf[o] = v[c];
+                        const float val = scaled ? v[c] * row_scale[m] : v[c];
+                        if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(val);
+                        else if (p.out_kind == kAddF32) red_add_f32(outf + o, val);
+                        else outf[o] = val;
                     }
                 }
             }
@@ -365,15 +432,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const float4 t = ld_shared_f4(recv + (uint32_t)(((src * units_per_owner + ul) * 32 + lane) * 16));
                     a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
                 }
-                const float v[4] = {a.x, a.y, a.z, a.w};
+                float v[4] = {a.x, a.y, a.z, a.w};
+                const bool scaled = p.scale_sumsq != nullptr;
+                const bool emits = p.out_kind == kAddF32 && p.emit_rows != nullptr;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int m = m0 + e;
+                    if (scaled && m < p.M) v[e] *= row_scale[m];
                     if (p.out_kind == kSwigluBF16) {
                         // lanes 0-15 hold gate values, lanes 16-31 the up values of the same outputs
                         const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
                         if ((lane & 16) == 0 && n < p.N && m < p.M)
                             outh[(size_t)m * (p.N >> 1) + (n >> 5) * 16 + (lane & 15)] = __float2bfloat16_rn(silu_mul(v[e], other));
+                    } else if (emits) {
+                        // (as in the unsplit epilogue: the updated row as bfloat16 and its squares summed over the warp's 32 features)
+                        float sq = 0.0f;
+                        if (n < p.N && m < p.M) {
+                            const size_t o = (size_t)m * p.N + n;
+                            const float xn = ((have_old && ul == warp - 2) ? x_old[e] : outf[o]) + v[e];
+                            outf[o] = xn;
+                            p.emit_rows[o] = __float2bfloat16_rn(xn);
+                            sq = xn * xn;
+                        }
+                        sq = warp_sum(sq);
+                        if (lane == 0 && n < p.N && m < p.M) p.emit_sumsq[(size_t)m * (p.N >> 5) + (n >> 5)] = sq;
                     } else if (n < p.N && m < p.M) {
                         const size_t o = (size_t)m * p.N + n;
                         if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[e]);
@@ -560,6 +642,20 @@ extern "C" int citlali_gemm_tc_plan(int M, int N, int K, int sm_count, int force
 // `force_splits` > 0 replaces the plan's K split (for tuning and tests; at most 8).
 extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                                int mode, int force_splits, int32_t* error_flag, int sm_count, cudaStream_t stream) {
+    return citlali_gemm_tc_normed(x, w, y, y_dtype, M, N, K, mode, force_splits, error_flag, sm_count, nullptr, nullptr,
+                                  nullptr, 0, 0, 0.0f, stream);
+}
+
+// citlali_gemm_tc for few rows of x (the form with the weights as the 128-row operand: see citlali_gemm_tc_plan) with a
+// layer norm's work in its epilogue.  `emit_rows` / `emit_sumsq` (both or neither; mode bit 0, N a multiple of 32): the
+// product is added to the float32 rows y as always, and the updated rows also go out as bfloat16 [M, N] with the sums of
+// their squares over each 32 consecutive features, float32 [M, N / 32].  `scale_sumsq` (float32 [M, scale_groups], the
+// sums of squares of the rows of x over groups of features): every result row m is multiplied by
+// rsqrt(sum of its groups / scale_dim + scale_eps) before it is stored, gated or added.
+extern "C" int citlali_gemm_tc_normed(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
+                                      int mode, int force_splits, int32_t* error_flag, int sm_count,
+                                      void* emit_rows, float* emit_sumsq, const float* scale_sumsq, int scale_groups,
+                                      int scale_dim, float scale_eps, cudaStream_t stream) {
     const bool accumulate = (mode & 1) != 0, swiglu = (mode & 2) != 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) {
@@ -584,8 +680,25 @@ extern "C" int citlali_gemm_tc(const void* x, const void* w, void* y, int y_dtyp
     }
     if (sm_count <= 0) sm_count = device_sm_count();
     const Plan pl = make_plan(M, N, K, sm_count, force_splits, swiglu);
+    const bool normed = emit_rows != nullptr || emit_sumsq != nullptr || scale_sumsq != nullptr;
+    if (normed) {
+        if (!pl.swapped) {
+            set_last_error("gemm_tc_normed: %d rows of x run the prompt form of the product, whose epilogue does no norm work", M);
+            return kBadShape;
+        }
+        if ((emit_rows == nullptr) != (emit_sumsq == nullptr) || (emit_rows != nullptr && (!accumulate || N % 32 != 0))) {
+            set_last_error("gemm_tc_normed: emitting needs both outputs, the adding mode and N a multiple of 32 (N %d)", N);
+            return kBadShape;
+        }
+        if (scale_sumsq != nullptr && (scale_groups <= 0 || scale_dim <= 0)) {
+            set_last_error("gemm_tc_normed: scaling needs the number of groups and the norm's width");
+            return kBadShape;
+        }
+    }
     if (runs_on_pairs(M, N, K, pl)) return citlali_gemm_tc_pair(x, w, y, y_dtype, M, N, K, mode, error_flag, stream);
     GemmParams p;
+    p.emit_rows = (__nv_bfloat16*)emit_rows; p.emit_sumsq = emit_sumsq;
+    p.scale_sumsq = scale_sumsq; p.scale_groups = scale_groups; p.scale_dim = scale_dim; p.scale_eps = scale_eps;
     p.M = M; p.N = N; p.K = K;
     p.splits = pl.splits;
     p.error_flag = error_flag;

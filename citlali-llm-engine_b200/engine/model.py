@@ -108,10 +108,14 @@ class DecoderModel:
         x = torch.empty((batch.rows, spec.hidden_size), dtype=torch.float32, device=ctx.device)
         ops.embed_rows(self.embedding, batch.tokens, x, ctx.error_flag,
                        1.0 if spec.embedding_scale is None else float(spec.embedding_scale))
+        batch.norm_carry = None
         for i, step in enumerate(spec.schedule):
             source = i if step.cache_of is None else step.cache_of
             view = cache.view(source) if cache.has_view(source) else None
+            # what the layer before left for this layer's first norm, if it left anything (parts/block.py)
+            batch.norm_carry_in, batch.norm_carry = batch.norm_carry, None
             self.layers[step.layer].forward(x, batch, view, write_cache=step.cache_of is None)
+        batch.norm_carry_in = batch.norm_carry = None
         wanted = int(batch.want_rows.numel())
         if wanted == 0:
             return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=ctx.device)

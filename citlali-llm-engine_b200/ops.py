@@ -360,9 +360,26 @@ def gemm_tc_accepts(x, w, y) -> bool:
             and x.is_contiguous() and w.is_contiguous() and y.is_contiguous())
 
 
-def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_splits=0):
+def norm_inputs(x: torch.Tensor, rows_out: torch.Tensor, sumsq: torch.Tensor):
+    """``rows_out = bfloat16(x)`` and ``sumsq[r, g]`` = the sum of squares of x[r]'s g-th group of 32 features."""
+    _need_cuda(x, rows_out, sumsq)
+    rows, hidden = x.shape
+    require(x.dtype == torch.float32 and rows_out.dtype == torch.bfloat16 and sumsq.dtype == torch.float32
+            and rows_out.shape == x.shape and sumsq.shape == (rows, hidden // 32), "norm_inputs: shapes or dtypes do not fit")
+    _check(lib().citlali_norm_inputs(_ptr(x), _ptr(rows_out), _ptr(sumsq), _i(rows), _i(hidden), _stream()), "norm_inputs")
+
+
+def gemm_tc_is_small_form(M: int, N: int, K: int, device) -> bool:
+    """Whether the product of this shape runs the form for few rows of x, whose epilogue can do a norm's work."""
+    return gemm_tc_plan(M, N, K, device)["swapped"]
+
+
+def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_splits=0, emit=None, row_scale=None):
     """``y = x . w^T`` on the tensor cores.  ``accumulate``: ``y`` (float32) ``+=``.  ``swiglu``: ``w``'s
-    rows alternate gate/up in runs of 16 and ``y`` is bfloat16 ``[M, N/2] = silu(gate) * up``."""
+    rows alternate gate/up in runs of 16 and ``y`` is bfloat16 ``[M, N/2] = silu(gate) * up``.
+    Few rows of x only: ``emit = (rows_bf16 [M, N], sumsq [M, N/32])`` (with ``accumulate``) also writes the updated
+    rows as bfloat16 and the sums of their squares over groups of 32 features; ``row_scale = (sumsq [M, groups], dim,
+    eps)`` multiplies result row m by ``rsqrt(sum(sumsq[m]) / dim + eps)``."""
     _need_cuda(x, w, y, error_flag)
     M, K = x.shape
     N = w.shape[0]
@@ -371,5 +388,25 @@ def gemm_tc(x, w, y, accumulate=False, error_flag=None, swiglu=False, force_spli
             "gemm_tc: operands must be contiguous bfloat16 with an inner size that is a multiple of 8")
     require(y.shape == (M, N // 2 if swiglu else N), "gemm_tc: the output's shape does not fit")
     mode = (1 if accumulate else 0) | (2 if swiglu else 0)
-    _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode),
-                                 _i(force_splits), _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")
+    if emit is None and row_scale is None:
+        _check(lib().citlali_gemm_tc(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode),
+                                     _i(force_splits), _ptr(error_flag), _i(sm_count(x.device)), _stream()), "gemm_tc")
+        return
+    emit_rows = emit_sumsq = scale_sumsq = None
+    groups = dim = 0
+    eps = 0.0
+    if emit is not None:
+        emit_rows, emit_sumsq = emit
+        _need_cuda(emit_rows, emit_sumsq)
+        require(emit_rows.dtype == torch.bfloat16 and emit_rows.shape == (M, N) and emit_sumsq.dtype == torch.float32
+                and emit_sumsq.shape == (M, N // 32), "gemm_tc: the emitted rows or their sums have the wrong shape or dtype")
+    if row_scale is not None:
+        scale_sumsq, dim, eps = row_scale
+        _need_cuda(scale_sumsq)
+        require(scale_sumsq.dtype == torch.float32 and scale_sumsq.dim() == 2 and scale_sumsq.shape[0] == M,
+                "gemm_tc: the sums of squares to scale by have the wrong shape or dtype")
+        groups = scale_sumsq.shape[1]
+    _check(lib().citlali_gemm_tc_normed(_ptr(x), _ptr(w), _ptr(y), _i(_dtype_code(y)), _i(M), _i(N), _i(K), _i(mode),
+                                        _i(force_splits), _ptr(error_flag), _i(sm_count(x.device)), _ptr(emit_rows),
+                                        _ptr(emit_sumsq), _ptr(scale_sumsq), _i(groups), _i(int(dim)), _f(float(eps)), _stream()),
+           "gemm_tc")

@@ -22,7 +22,7 @@ from .. import ops
 from ..cache import KVRequirement
 from ..errors import require
 from ..weights.loader import TensorSpec
-from .base import bind_gain, part_class, register_part
+from .base import NormedRows, bind_gain, part_class, register_part
 from .linear import DenseLinear
 
 
@@ -95,15 +95,27 @@ class GQAttention:
             self.inv_freq = torch.zeros(self.d // 2, dtype=torch.float32, device=ctx.device)   # no rotation by the kernel
         self.dtype = ctx.dtype
 
+    # ---- the norm in front of this part, done by its products ---------------------------------------------------
+    def can_absorb_norm(self) -> bool:
+        return self.qkv.can_take_normed_rows() and self.o.can_emit_normed_rows()
+
+    def fold_norm_gain(self, gain: torch.Tensor) -> None:
+        self.qkv.fold_input_gain(gain)
+
     # ---- one step ----------------------------------------------------------------------
-    def forward(self, h, batch, cache_view, residual, write_cache=True):
+    def forward(self, h, batch, cache_view, residual, write_cache=True, emit=None):
+        """``h``: the normed rows, or :class:`~.base.NormedRows` (few rows; after :meth:`fold_norm_gain`).  ``emit``: a pair
+        of buffers that the output projection fills with what the next norm needs of the updated residual rows."""
         require(cache_view is not None, f"{self.prefix}: attention needs a key/value cache")
         req = cache_view.requirement
         nkv_here = self.nkv if self.kv_projection else 0
         require(req.head_dim == self.d and req.num_kv_heads == self.nkv,
                 f"{self.prefix}: the cache holds {req.num_kv_heads} heads of {req.head_dim}, "
                 f"the layer has {self.nkv} of {self.d}")
-        qkv = self.qkv.forward(h)
+        if isinstance(h, NormedRows):
+            qkv = self.qkv.forward(h.rows, row_scale=h.scale)
+        else:
+            qkv = self.qkv.forward(h)
         store = write_cache and self.kv_projection
         common = (batch.row_slot, batch.row_pos, cache_view.page_table, cache_view.keys, cache_view.values,
                   cache_view.page_size, self.nq, nkv_here, self.d, float(self.eps or 0.0))
@@ -117,10 +129,10 @@ class GQAttention:
             self.position.apply(qkv, batch, self.nq, nkv_here, self.d)
             if store:
                 ops.qk_norm_rope_cache(qkv, None, None, self.inv_freq, self.rotary_dim, *common, write_cache=True)
-        out = torch.empty((batch.rows, self.nq * self.d), dtype=self.dtype, device=h.device)
+        out = torch.empty((batch.rows, self.nq * self.d), dtype=self.dtype, device=qkv.device)
         ops.attention(qkv, qkv.shape[1], cache_view, batch, out, self.nq, self.nkv, self.d,
                       int(self.window or 0), 1.0 / math.sqrt(self.d))
-        self.o.forward(out, accumulate_into=residual)
+        self.o.forward(out, accumulate_into=residual, emit=emit)
         return residual
 
 

@@ -78,6 +78,25 @@ class BuildContext:
 
 
 @dataclass
+class NormedRows:
+    """Rows that stand for ``rms_norm(x)`` without having been normalised: ``rows`` is bfloat16(x), ``sumsq[r, g]``
+    the sum of squares of x[r]'s g-th group of 32 features.  A product whose weights carry the norm's gain reads
+    ``rows`` and multiplies its result rows by ``rsqrt(sum(sumsq[r]) / dim + eps)``: the same numbers as the product
+    of the normalised rows, with the norm's kernel saved."""
+    rows: torch.Tensor
+    sumsq: torch.Tensor
+    dim: int
+    eps: float = 0.0
+
+    def with_eps(self, eps: float) -> "NormedRows":
+        return NormedRows(self.rows, self.sumsq, self.dim, float(eps))
+
+    @property
+    def scale(self):
+        return (self.sumsq, self.dim, self.eps)
+
+
+@dataclass
 class StepBatch:
     """One step's rows.  Sequence ``b`` owns rows ``seq_start[b] .. seq_start[b+1]-1``, which are
     its new tokens in order, at positions ``past[b] .. past[b]+n_new[b]-1`` of slot ``slots[b]``."""
@@ -91,6 +110,11 @@ class StepBatch:
     slots: List[int]
     past: List[int]
     n_new: List[int]
+    # A block that ends with a product which emitted what the next norm needs of the residual rows leaves it here
+    # (``norm_carry``); the model hands it to the next layer as ``norm_carry_in`` and clears it, so a layer that does
+    # not know of it breaks the chain instead of passing on something stale.
+    norm_carry: Optional["NormedRows"] = None
+    norm_carry_in: Optional["NormedRows"] = None
 
     @property
     def rows(self) -> int:

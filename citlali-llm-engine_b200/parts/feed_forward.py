@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import register_part
+from .base import NormedRows, register_part
 from .linear import DenseLinear
 
 _RUN = 16
@@ -36,12 +36,23 @@ class GatedSiluFeedForward:
         self.down.bind(weights, ctx)
         self.dtype = ctx.dtype
 
-    def forward(self, h, batch, residual):
-        act = self.gate_up.forward_gated(h, self.run)              # gate in the product's epilogue
-        if act is None:
-            act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
-            ops.swiglu(self.gate_up.forward(h), act, self.run)
-        self.down.forward(act, accumulate_into=residual)
+    def can_absorb_norm(self) -> bool:
+        return self.run == _RUN and self.gate_up.can_take_normed_rows() and self.down.can_emit_normed_rows()
+
+    def fold_norm_gain(self, gain: torch.Tensor) -> None:
+        self.gate_up.fold_input_gain(gain)
+
+    def forward(self, h, batch, residual, emit=None):
+        """``h``: the normed rows, or :class:`~.base.NormedRows` (few rows; after :meth:`fold_norm_gain`).  ``emit``: a pair
+        of buffers that the down projection fills with what the next norm needs of the updated residual rows."""
+        if isinstance(h, NormedRows):
+            act = self.gate_up.forward_gated(h.rows, self.run, row_scale=h.scale)
+        else:
+            act = self.gate_up.forward_gated(h, self.run)          # gate in the product's epilogue
+            if act is None:
+                act = torch.empty((h.shape[0], self.inter), dtype=self.dtype, device=h.device)
+                ops.swiglu(self.gate_up.forward(h), act, self.run)
+        self.down.forward(act, accumulate_into=residual, emit=emit)
         return residual
 
 

@@ -63,6 +63,25 @@ class DenseLinear:
         self.dtype = ctx.dtype
         self.error_flag = ctx.error_flag
 
+    # ---- a norm in front of this map, done by the map ----------------------------------------------------------
+    def can_take_normed_rows(self) -> bool:
+        """Bound in bfloat16 with shapes the tensor-core product takes: it can then read un-normalised rows and scale
+        its result rows instead (:class:`~.base.NormedRows`), once the norm's gain is folded into its weights."""
+        return (self.weight is not None and self.dtype == torch.bfloat16 and self.in_features % 32 == 0
+                and (self.interleave_run is None or (self.interleave_run == 16 and self.out_features % 32 == 0)))
+
+    def can_emit_normed_rows(self) -> bool:
+        return self.weight is not None and self.dtype == torch.bfloat16 and self.in_features % 8 == 0 and self.out_features % 32 == 0
+
+    def fold_input_gain(self, gain: torch.Tensor) -> None:
+        """W[n, k] *= gain[k] (in 32-bit, rounded once): x . (g * W)^T = (x * g) . W^T, so the norm in front of this map
+        no longer multiplies by its gain."""
+        require(gain.numel() == self.in_features, "the gain's length is not the map's input size")
+        w = self.weight
+        for r0 in range(0, w.shape[0], 8192):            # in pieces: no second copy of a large matrix in 32-bit
+            piece = w[r0:r0 + 8192]
+            piece.copy_((piece.float() * gain.float().to(w.device)[None, :]).to(w.dtype))
+
     def bind_shared(self, weight: torch.Tensor, ctx):
         """Use a matrix another part already holds (a head tied to the embedding)."""
         require(tuple(weight.shape) == (self.out_features, self.in_features), "shared matrix has the wrong shape")
@@ -74,20 +93,24 @@ class DenseLinear:
         return (self.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and x.is_contiguous() and x.data_ptr() % 16 == 0)
 
-    def forward_gated(self, x: torch.Tensor, run: int):
+    def forward_gated(self, x: torch.Tensor, run: int, row_scale=None):
         """For two stacked matrices interleaved in runs of 16 (gate, up): ``silu(gate) * up`` straight
-        from the product's epilogue, or ``None`` if this shape cannot (call :meth:`forward`)."""
+        from the product's epilogue, or ``None`` if this shape cannot (call :meth:`forward`).  ``row_scale``: see
+        :meth:`forward`."""
         rows = x.shape[0]
         if rows == 0 or run != 16 or self.out_features % 32 != 0 or not self.uses_tensor_cores(x):
+            require(row_scale is None, "this shape has no gate epilogue to scale rows in")
             return None
         act = torch.empty((rows, self.out_features // 2), dtype=torch.bfloat16, device=x.device)
-        ops.gemm_tc(x, self.weight, act, error_flag=self.error_flag, swiglu=True)
+        ops.gemm_tc(x, self.weight, act, error_flag=self.error_flag, swiglu=True, row_scale=row_scale)
         return act
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+                accumulate_into: Optional[torch.Tensor] = None, row_scale=None, emit=None) -> torch.Tensor:
         """``accumulate_into`` (float32 [rows, out]) receives ``+= x . W^T`` and is returned;
-        otherwise a new tensor of ``out_dtype`` (default: the compute dtype)."""
+        otherwise a new tensor of ``out_dtype`` (default: the compute dtype).  Few rows, tensor-core shapes only:
+        ``row_scale`` (``NormedRows.scale`` of the rows ``x`` stands for) scales the result rows; ``emit`` (a pair of
+        buffers, with ``accumulate_into``) receives the updated rows as bfloat16 and their sums of squares."""
         rows = x.shape[0]
         if accumulate_into is not None:
             y = accumulate_into
@@ -96,8 +119,10 @@ class DenseLinear:
         if rows == 0:
             return y
         if self.dtype == torch.bfloat16 and ops.gemm_tc_accepts(x, self.weight, y):
-            ops.gemm_tc(x, self.weight, y, accumulate=accumulate_into is not None, error_flag=self.error_flag)
+            ops.gemm_tc(x, self.weight, y, accumulate=accumulate_into is not None, error_flag=self.error_flag,
+                        row_scale=row_scale, emit=emit)
         else:
+            require(row_scale is None and emit is None, "only the tensor-core product does a norm's work in its epilogue")
             ops.gemm_simt(x, self.weight, y, accumulate=accumulate_into is not None)
         return y
 

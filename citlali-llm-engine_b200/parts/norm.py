@@ -19,6 +19,7 @@ class RMSNorm:
         self.eps = float(params["eps"])
         self.name = f"{prefix}.weight"
         self.gain = None
+        self.gain_downstream = False
 
     def tensor_specs(self):
         return [TensorSpec(self.name, (self.size,), "gain")]
@@ -26,6 +27,14 @@ class RMSNorm:
     def bind(self, weights, ctx):
         self.gain = bind_gain(weights, self.name, self.size, ctx)
         self.dtype = ctx.dtype
+
+    def gain_moves_downstream(self) -> torch.Tensor:
+        """The part behind this norm has multiplied its weights by the gain: from now on the norm only divides by the
+        root mean square (its kernel gets a gain of ones).  Returns the gain."""
+        gain = self.gain
+        self.gain = torch.ones_like(gain)
+        self.gain_downstream = True
+        return gain
 
     def forward(self, x: torch.Tensor, row_index=None) -> torch.Tensor:
         rows = x.shape[0] if row_index is None else row_index.numel()

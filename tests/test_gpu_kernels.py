@@ -244,6 +244,68 @@ def test_qk_norm_rope_cache_partial_rotation_and_keys_kept_in_the_row(nq, nkv, d
                                kp2, vp2, page, nq, nkv, d, eps)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(1, 64, 64, 0), (8, 4096, 1024, 0), (8, 4096, 1024, 1), (16, 96, 512, 2), (40, 160, 256, 4),
+                                          (64, 2048, 2048, 0), (128, 256, 1024, 8), (5, 32, 8, 0)])
+def test_products_that_do_a_norms_work(M, N, K, splits):
+    """A product that adds into the residual rows also emits those rows as bfloat16 with the sums of their squares over
+    groups of 32 features; the product behind it reads the rows un-normalised, with the norm's gain in its weights, and
+    scales its result rows: together the numbers of norm -> product, without the norm's kernel.  Split and unsplit."""
+    g = torch.Generator().manual_seed(M * N + K)
+    act = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    x0 = torch.randn(M, N, generator=g) * 3
+    x = x0.to(DEV).clone()
+    rows = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sums = torch.full((M, N // 32), float("nan"), dtype=torch.float32, device=DEV)
+    flag = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.gemm_tc(act.to(DEV), w1.to(DEV), x, accumulate=True, error_flag=flag, force_splits=splits, emit=(rows, sums))
+    want_x = x0.double() + act.double() @ w1.double().t()
+    close(x, want_x, torch.float32, scale=float(want_x.abs().max()))
+    assert torch.equal(rows, x.to(torch.bfloat16))                       # the very rows that were written, rounded once
+    want_sums = (x.double().cpu() ** 2).view(M, N // 32, 32).sum(-1)
+    assert float((sums.double().cpu() - want_sums).abs().max()) <= 1e-5 * float(want_sums.abs().max())
+    # the same call without emitting gives the same rows bit for bit
+    plain_x = x0.to(DEV).clone()
+    ops.gemm_tc(act.to(DEV), w1.to(DEV), plain_x, accumulate=True, error_flag=flag, force_splits=splits)
+    assert float((plain_x - x).abs().max()) <= 1e-6 * float(want_x.abs().max())
+    # the product behind: rms_norm(x) * gain . w2^T, as (x . (gain * w2)^T) * inv_rms(x), stored and gated
+    eps = 1e-5
+    gain = 1 + 0.3 * torch.randn(N, generator=g)
+    N2 = 96
+    w2 = (torch.randn(N2, N, generator=g) * 0.05).to(torch.bfloat16)
+    w2g = (w2.float() * gain[None, :]).to(torch.bfloat16)
+    # the oracle takes the operands as the kernel gets them (rows and weights already rounded to bfloat16), in the
+    # kernel's grouping: the plain norm's numbers up to that rounding of the operands
+    inv = torch.rsqrt((x.double().cpu() ** 2).sum(-1, keepdim=True) / N + eps)
+    want = (rows.double().cpu() @ w2g.double().t()) * inv
+    h = plain.rms_norm(x.double().cpu(), gain.double(), eps)
+    assert float((want - h @ w2.double().t()).abs().max()) <= 2e-2 * float(want.abs().max())
+    if N % 8 == 0:
+        y = torch.empty(M, N2, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc(rows, w2g.to(DEV), y, error_flag=flag, force_splits=splits if N >= 64 * max(splits, 1) else 0,
+                    row_scale=(sums, N, eps))
+        close(y, want, torch.bfloat16)
+        gated = torch.empty(M, N2 // 2, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc(rows, w2g.to(DEV), gated, error_flag=flag, swiglu=True, row_scale=(sums, N, eps))
+        gate = want.view(M, N2 // 32, 2, 16)
+        close(gated, plain.swiglu(gate[:, :, 0], gate[:, :, 1]).reshape(M, N2 // 2), torch.bfloat16)
+    assert flag.tolist() == [0, 0, 0, 0]
+
+
+def test_norm_inputs_and_refusals_of_the_normed_product():
+    x = torch.randn(7, 96) * 2
+    rows = torch.empty(7, 96, dtype=torch.bfloat16, device=DEV); sums = torch.empty(7, 3, device=DEV)
+    ops.norm_inputs(x.to(DEV), rows, sums)
+    assert torch.equal(rows.cpu(), x.to(torch.bfloat16))
+    assert float((sums.cpu().double() - (x.double() ** 2).view(7, 3, 32).sum(-1)).abs().max()) < 1e-4
+    big = torch.zeros(600, 64, dtype=torch.bfloat16, device=DEV); w = torch.zeros(4096, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(cb.CitlaliError, match="prompt form"):
+        ops.gemm_tc(big, w, torch.zeros(600, 4096, device=DEV), accumulate=True,
+                    emit=(torch.zeros(600, 4096, dtype=torch.bfloat16, device=DEV), torch.zeros(600, 128, device=DEV)))
+    with pytest.raises(cb.CitlaliError, match="multiple of 32"):
+        ops.norm_inputs(torch.zeros(2, 40, device=DEV), torch.zeros(2, 40, dtype=torch.bfloat16, device=DEV), torch.zeros(2, 1, device=DEV))
+
+
 def test_embedding_scale_and_logit_scale():
     table = torch.randn(50, 24)
     toks = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)

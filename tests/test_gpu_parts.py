@@ -206,6 +206,55 @@ def test_block_part(dtype):
     close(got, xd, dtype)
 
 
+@pytest.mark.parametrize("rows", [1, 20, 128, 129, 300])
+def test_block_with_its_norms_inside_the_products(rows):
+    """bfloat16, a width that is a multiple of 32: up to 128 rows the block's two norms run inside the products around
+    them (the gain folded into the weights behind it, the rows emitted un-normalised with their sums of squares); from
+    129 rows on the norm kernels run, without the gain.  Both against the plain block; and what one block leaves for
+    the next block's first norm is taken up by it."""
+    attn = {"hidden_size": 96, "num_heads": 6, "num_kv_heads": 2, "head_dim": 32, "qk_norm_eps": 1e-5,
+            "position": {"kind": "rotary_half_split", "theta": 3e4, "rotary_dim": 32}, "window": None}
+    spec = cb.LayerSpec(block="pre_norm_residual", parts={
+        "mixer_norm": cb.PartSpec("rms_norm", {"size": 96, "eps": 1e-5}, "n1"),
+        "mixer": cb.PartSpec("gqa_attention", dict(attn), "a"),
+        "feed_forward_norm": cb.PartSpec("rms_norm", {"size": 96, "eps": 2e-5}, "n2"),
+        "feed_forward": cb.PartSpec("gated_silu", {"hidden_size": 96, "intermediate_size": 160}, "mlp")})
+    dtype = torch.bfloat16
+    block = part_class("block", "pre_norm_residual")(spec)
+    h, w = handles(block, dtype, gain_spread=0.5)
+    block.bind(h, ctx_for(dtype))
+    assert block.norms_in_products and torch.equal(block.mixer_norm.gain, torch.ones_like(block.mixer_norm.gain))
+    cache = SequenceCache([block.cache_requirement()], 1, 512, 512, dtype, DEV)
+    slot = cache.acquire()
+    x = torch.randn(rows, 96) * 2
+    batch = pack_step([StepEntry(slot, [0] * rows, [])], [0], 10, DEV)
+    cache.reserve(slot, rows)
+    got = block.forward(x.to(DEV).clone(), batch, cache.view(0))
+    xd = x.double()
+    xd = xd + plain_attention_part(plain.rms_norm(xd, w["n1.weight"], 1e-5), w, attn)
+    xd = xd + plain.feed_forward(plain.rms_norm(xd, w["n2.weight"], 2e-5), w, "mlp")
+    close(got, xd, dtype)
+    carried = batch.norm_carry
+    if rows <= 128:
+        assert carried is not None and torch.equal(carried.rows, got.to(torch.bfloat16))
+        want = (got.double().cpu() ** 2).view(rows, 3, 32).sum(-1)
+        assert float((carried.sumsq.double().cpu() - want).abs().max()) <= 1e-5 * float(want.max())
+        # the same block again on the updated rows: with what it left itself, and without (the rows re-read)
+        cache.commit(slot, rows); cache.rewind(slot, 0)
+        batch.norm_carry_in, batch.norm_carry = carried, None
+        with_carry = block.forward(got.clone(), batch, cache.view(0))
+        batch.norm_carry_in = batch.norm_carry = None
+        without = block.forward(got.clone(), batch, cache.view(0))
+        assert float((with_carry - without).abs().max()) <= 1e-6 * float(without.abs().max())
+    else:
+        assert carried is None
+    # the 32-bit path keeps its norms as they are
+    block32 = part_class("block", "pre_norm_residual")(spec)
+    h32, _ = handles(block32, torch.float32, gain_spread=0.5)
+    block32.bind(h32, ctx_for(torch.float32))
+    assert not block32.norms_in_products
+
+
 def test_unknown_kinds_are_named():
     with pytest.raises(cb.CitlaliError, match="unknown mixer kind 'conv'.*gqa_attention"):
         part_class("mixer", "conv")
