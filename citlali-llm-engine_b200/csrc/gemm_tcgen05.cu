@@ -436,26 +436,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const bool scaled = p.scale_sumsq != nullptr;
                 const bool emits = p.out_kind == kAddF32 && p.emit_rows != nullptr;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int m = m0 + e;
-                    if (scaled && m < p.M) v[e] *= row_scale[m];
-                    if (p.out_kind == kSwigluBF16) {
-                        // lanes 0-15 hold gate values, lanes 16-31 the up values of the same outputs
-                        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
-                        if ((lane & 16) == 0 && n < p.N && m < p.M)
-                            outh[(size_t)m * (p.N >> 1) + (n >> 5) * 16 + (lane & 15)] = __float2bfloat16_rn(silu_mul(v[e], other));
-                    } else if (emits) {
-                        // (as in the unsplit epilogue: the updated row as bfloat16 and its squares summed over the warp's 32 features)
-                        float sq = 0.0f;
+                for (int e = 0; e < 4; ++e)
+                    if (scaled && m0 + e < p.M) v[e] *= row_scale[m0 + e];
+                if (emits) {
+                    // (as in the unsplit epilogue: the updated rows as bfloat16 and their squares summed over the warp's 32
+                    // features; the four rows' sums go through the shuffles side by side)
+                    float sq[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int m = m0 + e;
+                        sq[e] = 0.0f;
                         if (n < p.N && m < p.M) {
                             const size_t o = (size_t)m * p.N + n;
                             const float xn = ((have_old && ul == warp - 2) ? x_old[e] : outf[o]) + v[e];
                             outf[o] = xn;
                             p.emit_rows[o] = __float2bfloat16_rn(xn);
-                            sq = xn * xn;
+                            sq[e] = xn * xn;
                         }
-                        sq = warp_sum(sq);
-                        if (lane == 0 && n < p.N && m < p.M) p.emit_sumsq[(size_t)m * (p.N >> 5) + (n >> 5)] = sq;
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sq[e] += __shfl_xor_sync(0xffffffffu, sq[e], off);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (lane == 0 && n < p.N && m0 + e < p.M) p.emit_sumsq[(size_t)(m0 + e) * (p.N >> 5) + (n >> 5)] = sq[e];
+                    continue;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int m = m0 + e;
+                    if (p.out_kind == kSwigluBF16) {
+                        // lanes 0-15 hold gate values, lanes 16-31 the up values of the same outputs
+                        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+                        if ((lane & 16) == 0 && n < p.N && m < p.M)
+                            outh[(size_t)m * (p.N >> 1) + (n >> 5) * 16 + (lane & 15)] = __float2bfloat16_rn(silu_mul(v[e], other));
                     } else if (n < p.N && m < p.M) {
                         const size_t o = (size_t)m * p.N + n;
                         if (p.out_kind == kStoreBF16) outh[o] = __float2bfloat16_rn(v[e]);
