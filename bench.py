@@ -324,6 +324,9 @@ def main():
     ap.add_argument("--workload", type=int, default=2,
                     help="which of BASELINE.json's configs to run: 2 (the benchmark configuration) or a batch workload (3, 4)")
     ap.add_argument("--repetitions", type=int, default=5, help="timed repetitions (the median is reported)")
+    ap.add_argument("--run-from", type=int, default=None,
+                    help="length of the prompts of the decode runs (default: the prefill length, 2,048); close to the context "
+                         "length it makes a short run, as a profiler capture needs")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -406,7 +409,8 @@ def main():
 
     def decode_run(batch):
         slots = [session.acquire() for _ in range(batch)]
-        prompts = [[rng.randrange(vocab) for _ in range(prefill_tokens)] for _ in range(batch)]
+        run_from = min(args.run_from or prefill_tokens, context - (W + K) - 8)
+        prompts = [[rng.randrange(vocab) for _ in range(run_from)] for _ in range(batch)]
         a, b = ev(), ev()
         torch.cuda.synchronize()
         a.record()
@@ -414,9 +418,9 @@ def main():
         b.record()
         torch.cuda.synchronize()
         out = {"prefill_ms": a.elapsed_time(b)}
-        total = context - prefill_tokens                       # decode steps: positions prefill_tokens .. context-1
-        window = min(64, total // 4)
-        marks = {"ctx%d" % prefill_tokens: 0, "ctx%d" % ((prefill_tokens + context) // 2): total // 2 - window // 2,
+        total = context - run_from                             # decode steps: positions run_from .. context-1
+        window = max(1, min(64, total // 4))
+        marks = {"ctx%d" % run_from: 0, "ctx%d" % ((run_from + context) // 2): total // 2 - window // 2,
                  "ctx%d" % context: total - window}
         starts = {max(at, 1): name for name, at in marks.items()}
         ends = {max(at, 1) + window - 1: name for name, at in marks.items()}
@@ -493,7 +497,7 @@ def main():
                 ctx_len = int(name[3:]) + (32 if int(name[3:]) < context else -32)
                 point_fracs[f"decode_b{bsz}_{name}"] = round(step_bytes(bsz, ctx_len) * v / bsz / 1e9 / pk["hbm_gbs"], 4)
         points[f"decode_b{bsz}_run"] = r["run_tok_s"]
-        points[f"prefill_b{bsz}_tok_s"] = bsz * prefill_tokens / (r["prefill_ms"] / 1e3)
+        points[f"prefill_b{bsz}_tok_s"] = bsz * min(args.run_from or prefill_tokens, context - (W + K) - 8) / (r["prefill_ms"] / 1e3)
 
     kernels = {} if args.skip_points else time_kernels(session, cb, ops, torch, cfg, args.batch, context, prefill_tokens, pk)
     clock_record = clocks.stop()
@@ -584,9 +588,15 @@ def time_kernels(session, cb, ops, torch, cfg, batch, context, prefill_tokens, p
         views = [cache.view(i) for i in range(len(blocks))]
         m = [b.mixer for b in blocks]
         f = [b.feed_forward for b in blocks]
+        # decoding runs the layer norms inside the products around them (parts/block.py): the products are timed in
+        # the form the step runs, the norm kernel remains for the first layer's rows and before the head
+        fused = what == "decode" and getattr(blocks[0], "norms_in_products", False)
+        sums = torch.ones(rows, H // 32, device=dev)
+        emit = (torch.empty(rows, H, dtype=torch.bfloat16, device=dev), torch.empty(rows, H // 32, device=dev))
+        scale = (sums, H, 1e-6)
         us = {
             "norm": sweep(lambda i: blocks[i].mixer_norm.forward(x)),
-            "qkv": sweep(lambda i: m[i].qkv.forward(h)),
+            "qkv": sweep(lambda i: m[i].qkv.forward(h, row_scale=scale if fused else None)),
             "norm_rope_cache": sweep(lambda i: ops.qk_norm_rope_cache(
                 qkv, m[i].q_gain, m[i].k_gain, m[i].inv_freq, m[i].rotary_dim, step.row_slot, step.row_pos, views[i].page_table,
                 views[i].keys, views[i].values, views[i].page_size, nq, nkv, d, float(m[i].eps))),
@@ -598,9 +608,9 @@ def time_kernels(session, cb, ops, torch, cfg, batch, context, prefill_tokens, p
                                                                    views[i].page_table, step.seq_start, step.seq_slot, step.seq_past,
                                                                    attn_out, 1, rows, nq, nkv, d, views[i].page_size, 0,
                                                                    1.0 / math.sqrt(d), model.ctx.error_flag))),
-            "output": sweep(lambda i: m[i].o.forward(o_in, accumulate_into=x)),
-            "gate_up": sweep(lambda i: f[i].gate_up.forward_gated(h, f[i].run)),
-            "down": sweep(lambda i: f[i].down.forward(act, accumulate_into=x)),
+            "output": sweep(lambda i: m[i].o.forward(o_in, accumulate_into=x, emit=emit if fused else None)),
+            "gate_up": sweep(lambda i: f[i].gate_up.forward_gated(h, f[i].run, row_scale=scale if fused else None)),
+            "down": sweep(lambda i: f[i].down.forward(act, accumulate_into=x, emit=emit if fused else None)),
         }
         if what == "decode":
             hw = torch.randn(batch, H, device=dev).to(torch.bfloat16)
@@ -622,7 +632,8 @@ def time_kernels(session, cb, ops, torch, cfg, batch, context, prefill_tokens, p
                 out[f"prefill_{k}"] = {"us": round(t, 1)}
                 if k in need:
                     out[f"prefill_{k}"]["frac"] = round(need[k] / (t * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
-    out["note"] = ("us per launch in a replayed sweep over the layers, best of 4; decode frac = bytes the kernel must read / time / "
+    out["note"] = ("us per launch in a replayed sweep over the layers, best of 4; decode products in the form the step runs "
+                   "(the layer norms' work in their epilogues), the norm kernel itself runs twice a step; decode frac = bytes the kernel must read / time / "
                    "copy bandwidth, prefill frac = FLOPs / time / bf16 burst peak")
     return out
 
