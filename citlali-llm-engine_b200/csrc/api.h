@@ -65,14 +65,19 @@ int citlali_attention_rows(const void* q, int q_stride, int dtype,
 
 // Attention of single new tokens (bfloat16) split over the context; positions are read on the
 // device, `max_positions` bounds them and fixes the grid.  `partial` is float scratch of
-// citlali_attention_decode_scratch_floats(...) elements.
+// citlali_attention_decode_scratch_floats(...) elements.  `counters` (may be nullptr): `counter_ints` 32-bit
+// words, at least rows * nkv * ceil((nq / nkv) / 16), zero before the first call; every call leaves them zero.
+// With them, a step of many rows deals the pages of its long rows out to several blocks by the rows' lengths.
 size_t citlali_attention_decode_scratch_floats(int rows, int nq, int head_dim, int page_size, int max_positions);
 int citlali_attention_decode(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                              const int32_t* page_table, int page_table_stride,
                              const int32_t* row_slot, const int32_t* row_pos,
                              void* out, int out_stride, float* partial, size_t partial_floats,
+                             int32_t* counters, size_t counter_ints,
                              int rows, int nq, int nkv, int head_dim, int page_size, int window,
                              int max_positions, float scale, cudaStream_t stream);
+void citlali_attention_decode_set_split(int split);
+void citlali_attention_decode_set_by_length(int on, int run_scale_q8);
 
 // Causal attention of runs of new tokens (bfloat16, pages of 64) on the tensor cores.  Sequence b
 // owns rows seq_start[b] .. seq_start[b+1]-1 at positions seq_past[b] + i of slot seq_slot[b].

@@ -222,47 +222,65 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, uint32_t rank, flo
 // units), and the blocks of a cluster send their runs of a head to the block that merges that head.
 constexpr int kMaxClusterBlocks = 16;     // blocks per (sequence, head group): a cluster, at most the non-portable size
 
+// One head's (m, l, O) of `runs` consecutive runs of its keys ([run][D + 2] at `base`, m in log2 units), merged in run
+// order into the head's output.  kFromL2: the runs were written by other blocks to global memory (read past L1).
+template <int kBlocks, int D, bool kFromL2>
+__device__ __forceinline__ void merge_runs(const float* base, int runs, __nv_bfloat16* out_head, int tid) {
+    auto at = [&](size_t i) { return kFromL2 ? __ldcg(base + i) : base[i]; };
+    float mz[kBlocks], wz[kBlocks];
+#pragma unroll
+    for (int z = 0; z < kBlocks; ++z) {
+        mz[z] = z < runs ? at((size_t)z * (D + 2)) : -INFINITY;
+        wz[z] = z < runs ? at((size_t)z * (D + 2) + 1) : 0.0f;           // l for now
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int z = 0; z < kBlocks; ++z) M = fmaxf(M, mz[z]);
+    float L = 0.0f;
+#pragma unroll
+    for (int z = 0; z < kBlocks; ++z) {
+        const float f = mz[z] == -INFINITY ? 0.0f : exp2f(mz[z] - M);
+        if (mz[z] != -INFINITY) L = fmaf(wz[z], f, L);
+        wz[z] = f;
+    }
+    const float inv = 1.0f / L;
+    for (int i = tid; i < D; i += 128) {
+        float a = 0.0f;
+#pragma unroll
+        for (int z = 0; z < kBlocks; ++z)
+            if (z < runs && mz[z] != -INFINITY) a = fmaf(at((size_t)z * (D + 2) + 2 + i), wz[z], a);
+        out_head[i] = __float2bfloat16_rn(a * inv);
+    }
+}
+
 // Block `rank` of a cluster merges heads rank, rank + split, ... over the (m, l, O) of all blocks' runs, which
 // they have sent to `gathered` ([head / split][sender][D + 2]), in rank order.
 template <int kBlocks, int D>
 __device__ __forceinline__ void merge_gathered_heads(const float* gathered, __nv_bfloat16* out_row, int rank, int split, int heads_here, int tid) {
-    for (int h = rank; h < heads_here; h += split) {
-        const float* base = gathered + (size_t)((h / split) * split) * (D + 2);
-        float mz[kBlocks], wz[kBlocks];
-#pragma unroll
-        for (int z = 0; z < kBlocks; ++z) {
-            mz[z] = z < split ? base[(size_t)z * (D + 2)] : -INFINITY;
-            wz[z] = z < split ? base[(size_t)z * (D + 2) + 1] : 0.0f;           // l for now
-        }
-        float M = -INFINITY;
-#pragma unroll
-        for (int z = 0; z < kBlocks; ++z) M = fmaxf(M, mz[z]);
-        float L = 0.0f;
-#pragma unroll
-        for (int z = 0; z < kBlocks; ++z) {
-            const float f = mz[z] == -INFINITY ? 0.0f : exp2f(mz[z] - M);
-            if (mz[z] != -INFINITY) L = fmaf(wz[z], f, L);
-            wz[z] = f;
-        }
-        const float inv = 1.0f / L;
-        for (int i = tid; i < D; i += 128) {
-            float a = 0.0f;
-#pragma unroll
-            for (int z = 0; z < kBlocks; ++z)
-                if (z < split && mz[z] != -INFINITY) a = fmaf(base[(size_t)z * (D + 2) + 2 + i], wz[z], a);
-            out_row[(size_t)h * D + i] = __float2bfloat16_rn(a * inv);
-        }
-    }
+    for (int h = rank; h < heads_here; h += split)
+        merge_runs<kBlocks, D, false>(gathered + (size_t)((h / split) * split) * (D + 2), split, out_row + (size_t)h * D, tid);
 }
 
-template <int D, int kStagesKV>
+constexpr int kMaxRunsByLength = 8;      // blocks a row's keys are dealt to at most when the rows' lengths decide
+constexpr int kMinRunTiles = 16;         // no run shorter than this many pages (measured: runs of 8 cost more than they balance)
+
+//
+// kByLength (many rows, no clusters; grid = head tiles x rows x runs, so that the blocks with nothing to do come
+// last): the rows of a step can differ in length by an order of magnitude, and a block that walks the longest row
+// alone is still walking when the others are done.  When the longest row has more than 1.3 times the mean number of
+// pages, a row's pages are dealt to ceil(row's pages / (mean pages x run_scale_q8 / 256)) blocks, at most
+// gridDim.z; a row's blocks write their (m, l, O) to `partial` ([row][head][run][D + 2]) and count themselves on
+// counters[row, head tile]; the block that counts last merges the runs in run order and puts the counter back to
+// zero.  Nobody waits for anybody.  Rows of about equal lengths keep one block each and nothing is merged.  The
+// number of runs depends on the lengths in the step, which are read on the device: the launch does not.
+template <int D, int kStagesKV, bool kByLength>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                            const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                            const int32_t* __restrict__ page_table, int page_table_stride,
                            const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
                            __nv_bfloat16* __restrict__ out, int out_stride, int nq, int nkv, int window,
-                           float scale_log2) {
+                           float scale_log2, float* __restrict__ partial, int* __restrict__ counters, int run_scale_q8) {
     using namespace fa;
     constexpr int kPage = 64;
     constexpr int kRowBytes = D * 2 + 16;
@@ -273,17 +291,46 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const uint32_t s_k = s_q + 16 * kRowBytes, s_v = s_k + kStagesKV * kTileBytes;
 
     dependents_may_launch();
-    const int split = gridDim.x, rank = blockIdx.x;      // the blocks of a (sequence, head group) are one cluster
+    int split = kByLength ? gridDim.z : gridDim.x;       // the blocks of a (sequence, head group) are one cluster
+    const int rank = kByLength ? blockIdx.z : blockIdx.x;
+    const int head_tile = kByLength ? blockIdx.x : blockIdx.y;
     const int group = nq / nkv;
     const int row_tiles = (group + 15) / 16;
-    const int g = blockIdx.y / row_tiles;
-    const int head0 = g * group + (blockIdx.y % row_tiles) * 16;
+    const int g = head_tile / row_tiles;
+    const int head0 = g * group + (head_tile % row_tiles) * 16;
     const int heads_here = min(16, g * group + group - head0);
-    const int row = blockIdx.z;
+    const int row = kByLength ? blockIdx.y : blockIdx.z;
     const int pos = row_pos[row];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     // the visible pages are cut into `split` runs of equal length; this block takes run `rank` (it may be empty)
     const int first_page = lo / kPage, last_page = pos / kPage;
+    if constexpr (kByLength) {
+        // pages visible to all rows of the step (every warp adds them up for itself), their mean, this row's runs
+        const int rows = gridDim.y;
+        int total = 0, longest = 0;
+        for (int r = threadIdx.x & 31; r < rows; r += 32) {
+            const int p = row_pos[r];
+            const int l = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+            const int pages = p / kPage - l / kPage + 1;
+            total += pages;
+            longest = max(longest, pages);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            total += __shfl_xor_sync(0xffffffffu, total, o);
+            longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+        }
+        if ((long)longest * rows * 10 <= (long)total * 13) {
+            split = 1;                                   // about equal lengths: a block a row
+        } else {
+            // run length: the mean times run_scale_q8 / 256, at least kMinRunTiles
+            const long scaled = ((long)total * run_scale_q8 + (long)rows * 256 - 1) / ((long)rows * 256);
+            const int run = scaled > kMinRunTiles ? (int)scaled : kMinRunTiles;
+            const int mine = last_page - first_page + 1;
+            split = min((int)gridDim.z, (mine + run - 1) / run);
+        }
+        if (rank >= split) return;
+    }
     const int per_block = (last_page - first_page + split) / split;
     const int tile_lo = first_page + rank * per_block, tile_hi = min(tile_lo + per_block - 1, last_page);
     const int32_t* pages = page_table + (size_t)row_slot[row] * page_table_stride;
@@ -392,7 +439,7 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     cp_async_wait<0>();
     // This block no longer reads its tile buffers: it says so to the cluster at once and waits for the others
     // only before it writes into theirs.
-    if (split > 1) cluster_arrive();
+    if (!kByLength && split > 1) cluster_arrive();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
@@ -442,6 +489,30 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
         return;
     }
+    if constexpr (kByLength) {
+        __shared__ int counted_last;
+        const int chunks = gridDim.z;
+        float* mine = partial + (((size_t)row * nq + head0) * chunks + rank) * (D + 2);
+        for (int e = tid; e < elems; e += 128) {
+            const int h = e / (D + 2), i = e % (D + 2);
+            __stcg(mine + (size_t)h * chunks * (D + 2) + i, folded(e));
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int* counter = counters + (size_t)row * gridDim.x + head_tile;
+            const int before = atomicAdd(counter, 1);
+            counted_last = before == split - 1;
+            if (counted_last) *counter = 0;              // every block of the row has counted: ready for the next launch
+        }
+        __syncthreads();
+        if (!counted_last) return;
+        __threadfence();
+        for (int h = 0; h < heads_here; ++h)
+            merge_runs<kMaxRunsByLength, D, true>(partial + ((size_t)row * nq + head0 + h) * chunks * (D + 2), split,
+                                                  out_row + (size_t)h * D, tid);
+        return;
+    }
     // Head h is merged by block h % split.  Every block sends its (m, l, O) of a head into that block's shared
     // memory, to [h / split][sender]: once all blocks are past their tiles (the barrier they arrived at
     // above), the space behind a block's parked rows is free.  After one more barrier a block finds all
@@ -463,15 +534,19 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
 static int g_forced_split = 0;     // > 0: blocks per (sequence, head group), for tuning
 
-template <int D, int kStagesKV>
+static int g_run_scale_q8 = 160;   // by-length kernel: a run's length in 1/256 of the mean length of the step's rows
+static int g_by_length = 1;        // 0: never deal a row's pages out by length
+
+template <int D, int kStagesKV, bool kByLength = false>
 static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                      int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
-                     int rows, int nq, int nkv, int window, float scale, int split, cudaStream_t stream) {
+                     int rows, int nq, int nkv, int window, float scale, int split, cudaStream_t stream,
+                     float* partial = nullptr, int* counters = nullptr) {
     constexpr int tiles = (16 + 2 * kStagesKV * 64) * (D * 2 + 16);
     // the query rows, the four warps' parked rows, and behind them what the cluster's blocks send (at most 31 runs)
     constexpr int park = 16 * (D * 2 + 16) + (4 * 16 + 32) * (D + 2) * 4;
     constexpr int smem = tiles > park ? tiles : park;
-    auto kernel = attention_decode_tc_kernel<D, kStagesKV>;
+    auto kernel = attention_decode_tc_kernel<D, kStagesKV, kByLength>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -484,10 +559,11 @@ static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, con
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return (int)e;
     }
-    dim3 grid(split, kv_tiles, rows);
-    launch_kernel_clustered(kernel, grid, 128, smem, split, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool,
-                            (const __nv_bfloat16*)v_pool, page_table, page_table_stride, row_slot, row_pos,
-                            (__nv_bfloat16*)out, out_stride, nq, nkv, window, scale * 1.4426950408889634f);
+    const dim3 grid = kByLength ? dim3(kv_tiles, rows, split) : dim3(split, kv_tiles, rows);
+    launch_kernel_clustered(kernel, grid, 128, smem, kByLength ? 1 : split, stream, (const __nv_bfloat16*)q, q_stride,
+                            (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, page_table_stride,
+                            row_slot, row_pos, (__nv_bfloat16*)out, out_stride, nq, nkv, window,
+                            scale * 1.4426950408889634f, partial, counters, g_run_scale_q8);
     return CITLALI_LAUNCH_CHECK();
 }
 
@@ -498,7 +574,8 @@ static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, con
 template <int D>
 static int launch_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                      int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
-                     int rows, int nq, int nkv, int window, float scale, cudaStream_t stream) {
+                     int rows, int nq, int nkv, int window, float scale, cudaStream_t stream,
+                     float* partial, size_t partial_floats, int* counters, size_t counter_ints) {
     const int group = nq / nkv;
     const long pairs = (long)rows * nkv * ((group + 15) / 16);
     int split = 1;
@@ -509,6 +586,17 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
     // against 56 at 32,000, but 7.8 against 5.9 at 500; the table's width, unlike the lengths, is fixed for a session.
     if (pairs * 16 <= 128 && page_table_stride > 128) split = 16;
     if (g_forced_split > 0) split = g_forced_split > kMaxClusterBlocks ? kMaxClusterBlocks : g_forced_split;
+    // Many rows (one block each would fill the GPU): the rows' lengths decide, on the device, which of them get
+    // more than one block.  Needs the scratch for their partial results and the zeroed counters.
+    if (split == 1 && g_by_length && partial != nullptr && counters != nullptr && (size_t)pairs <= counter_ints) {
+        int runs = page_table_stride / kMinRunTiles;
+        if (runs > kMaxRunsByLength) runs = kMaxRunsByLength;
+        while (runs > 1 && (size_t)rows * nq * runs * (D + 2) > partial_floats) --runs;
+        if (runs > 1)
+            return launch_tc_stages<D, kKvStages, true>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot,
+                                                        row_pos, out, out_stride, rows, nq, nkv, window, scale, runs, stream,
+                                                        partial, counters);
+    }
     // with at most one block per SM there is shared memory for six tiles in flight (head sizes up to 128)
     if constexpr (D <= 128) {
         if (pairs * split <= 80)          // more blocks than that, each filling an SM, no longer fit cluster by cluster
@@ -557,6 +645,13 @@ using namespace citlali;
 // > 0: the tensor-core kernel uses this many blocks per (sequence, head group) (1, 2, 4, 8 or 16); 0: its own choice.
 extern "C" void citlali_attention_decode_set_split(int split) { g_forced_split = split; }
 
+// Tuning of the kernel that deals a long row's pages out by length (steps of many rows): on/off, and a run's
+// length in 1/256 of the mean length of the step's rows (256: the mean itself; 0 leaves it as it is).
+extern "C" void citlali_attention_decode_set_by_length(int on, int run_scale_q8) {
+    g_by_length = on;
+    if (run_scale_q8 > 0) g_run_scale_q8 = run_scale_q8;
+}
+
 // Scratch for the partials of `rows` single-token rows whose positions stay below
 // `max_positions`: floats.
 extern "C" size_t citlali_attention_decode_scratch_floats(int rows, int nq, int head_dim, int page_size, int max_positions) {
@@ -567,11 +662,15 @@ extern "C" size_t citlali_attention_decode_scratch_floats(int rows, int nq, int 
 
 // Attention of `rows` single new tokens (bfloat16).  q rows are `q_stride` elements apart;
 // positions and slots are read on the device; `max_positions` bounds the positions and fixes
-// the grid.  `partial` holds citlali_attention_decode_scratch_floats(...) floats.
+// the grid.  `partial` holds citlali_attention_decode_scratch_floats(...) floats.  `counters`: `counter_ints`
+// 32-bit words (one per row and key/value head is enough) that are ZERO before the first call and that every call
+// leaves zero; calls that share them must not overlap on the device.  Without them (nullptr) long rows of a
+// large step are not dealt out by length.
 extern "C" int citlali_attention_decode(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                         const int32_t* page_table, int page_table_stride,
                                         const int32_t* row_slot, const int32_t* row_pos,
                                         void* out, int out_stride, float* partial, size_t partial_floats,
+                                        int32_t* counters, size_t counter_ints,
                                         int rows, int nq, int nkv, int head_dim, int page_size, int window,
                                         int max_positions, float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
@@ -594,10 +693,11 @@ extern "C" int citlali_attention_decode(const void* q, int q_stride, const void*
         default: tensor_cores = false;
     }
     if (tensor_cores) {
-        // pages of 64 and a head size the tensor-core kernel has: its blocks merge their partial results
-        // through distributed shared memory, the scratch is not used
+        // pages of 64 and a head size the tensor-core kernel has: in steps of few rows its blocks merge their
+        // partial results through distributed shared memory and the scratch is not used
 #define CITLALI_TC(DD) case DD: return launch_tc<DD>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, \
-                                                      out, out_stride, rows, nq, nkv, window, scale, stream)
+                                                      out, out_stride, rows, nq, nkv, window, scale, stream, partial, \
+                                                      partial_floats, counters, counter_ints)
         switch (head_dim) {
             CITLALI_TC(16); CITLALI_TC(32); CITLALI_TC(48); CITLALI_TC(64); CITLALI_TC(80); CITLALI_TC(96); CITLALI_TC(112);
             CITLALI_TC(128); CITLALI_TC(256);

@@ -14,11 +14,14 @@
 namespace citlali {
 
 static __device__ __align__(256) float g_no_alloc_scratch[CITLALI_NO_ALLOC_SCRATCH_FLOATS];
+// Counters of the kernel that deals long rows out by length: zero when the library is loaded, and every call
+// leaves them zero.
+static __device__ __align__(256) int g_no_alloc_counters[CITLALI_NO_ALLOC_COUNTER_INTS];
 
 // Device code may name the array directly.  This kernel is never launched; it keeps the array
 // in the device image even though no other device code in this file refers to it.
 __global__ void no_alloc_scratch_anchor(float* out) {
-    if (out != nullptr) out[0] = g_no_alloc_scratch[0];
+    if (out != nullptr) out[0] = g_no_alloc_scratch[0] + (float)g_no_alloc_counters[0];
 }
 
 constexpr int kMaxDevices = 64;
@@ -26,9 +29,10 @@ constexpr int kMaxDevices = 64;
 // both look the address up and both store the same value: harmless, and the slot is atomic so that
 // neither reads a torn pointer.
 static std::atomic<float*> g_scratch_address[kMaxDevices];
+static std::atomic<int*> g_counters_address[kMaxDevices];
 
 // The device address of the array on the current device; looked up on the first call per device.
-static int scratch_for_current_device(float** ptr) {
+static int scratch_for_current_device(float** ptr, int** counters) {
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
@@ -48,7 +52,20 @@ static int scratch_for_current_device(float** ptr) {
         g_scratch_address[device].store(address, std::memory_order_release);
         known = address;
     }
+    int* known_counters = g_counters_address[device].load(std::memory_order_acquire);
+    if (known_counters == nullptr) {
+        int* address = nullptr;
+        e = cudaGetSymbolAddress((void**)&address, g_no_alloc_counters);
+        if (e != cudaSuccess) {
+            set_last_error("attention_decode_no_alloc: cudaGetSymbolAddress (counters) failed on device %d: %s", device,
+                           cudaGetErrorString(e));
+            return (int)e;
+        }
+        g_counters_address[device].store(address, std::memory_order_release);
+        known_counters = address;
+    }
     *ptr = known;
+    *counters = known_counters;
     return 0;
 }
 
@@ -75,10 +92,18 @@ extern "C" int citlali_attention_decode_no_alloc(const void* q, int q_stride, co
                        rows, nq, head_dim, max_positions, need, (unsigned)CITLALI_NO_ALLOC_SCRATCH_FLOATS);
         return kTooLarge;
     }
+    // one counter per row and group of 16 query heads of a key/value head: never more than rows * nq
+    if ((size_t)rows * (size_t)nq > (size_t)CITLALI_NO_ALLOC_COUNTER_INTS) {
+        set_last_error("attention_decode_no_alloc: %d rows x %d heads exceed the %u built-in counters", rows, nq,
+                       (unsigned)CITLALI_NO_ALLOC_COUNTER_INTS);
+        return kTooLarge;
+    }
     float* scratch = nullptr;
-    const int rc = scratch_for_current_device(&scratch);
+    int* counters = nullptr;
+    const int rc = scratch_for_current_device(&scratch, &counters);
     if (rc) return rc;
     return citlali_attention_decode(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, out,
-                                    out_stride, scratch, (size_t)CITLALI_NO_ALLOC_SCRATCH_FLOATS, rows, nq, nkv, head_dim,
+                                    out_stride, scratch, (size_t)CITLALI_NO_ALLOC_SCRATCH_FLOATS, counters,
+                                    (size_t)CITLALI_NO_ALLOC_COUNTER_INTS, rows, nq, nkv, head_dim,
                                     page_size, window, max_positions, scale, stream);
 }

@@ -11,15 +11,17 @@
 //
 // It computes exactly what citlali_attention_decode computes, with the same kernels, but the
 // float scratch that holds the per-chunk partial results lives in a fixed array inside the
-// library instead of being passed in.  (For pages of 64 keys and the head sizes of the
-// tensor-core kernel the blocks exchange their partial results through shared memory and the
-// array is not touched; the limit below is checked all the same.)
+// library instead of being passed in, and so do the counters that a step of many rows uses.
+// (For pages of 64 keys, the head sizes of the tensor-core kernel and few rows the blocks
+// exchange their partial results through shared memory and the arrays are not touched; the
+// limit below is checked all the same.)
 //
 //   Limit.  The array holds CITLALI_NO_ALLOC_SCRATCH_FLOATS floats (4 MiB).  A call needs
 //   rows * nq * ceil(max_positions / (2 * page_size)) * (head_dim + 2) floats; a call that
 //   needs more is refused with a negative return code and a message (citlali_last_error),
 //   and nothing is launched.  Every GPU that loads the library holds these 4 MiB until the
-//   process exits.
+//   process exits.  Beside it lie CITLALI_NO_ALLOC_COUNTER_INTS 32-bit counters (256 KiB), one
+//   per row and group of query heads; a call of more rows x heads than that is refused likewise.
 //
 //   First call.  The first call on each device looks up the array's device address
 //   (cudaGetSymbolAddress) and remembers it.  Make that first call outside any stream
@@ -29,8 +31,10 @@
 //
 //   Sharing.  All calls on a device share the one array, and it keeps whatever the last call
 //   left in it.  Nothing in it has to start at zero: every partial a call reads was written by
-//   that same call first.  But two calls whose kernels overlap on the GPU (different streams,
-//   or graphs replayed concurrently) race on it; issue them on one stream, or order them.
+//   that same call first.  The counters are zero when the library is loaded, and every call
+//   that finishes leaves them zero.  But two calls whose kernels overlap on the GPU (different
+//   streams, or graphs replayed concurrently) race on both; issue them on one stream, or
+//   order them.
 //
 //   It calls no cudaMalloc, cudaFree or any other allocating routine.
 #pragma once
@@ -38,12 +42,13 @@
 #include <stdint.h>
 
 #define CITLALI_NO_ALLOC_SCRATCH_FLOATS (1u << 20)
+#define CITLALI_NO_ALLOC_COUNTER_INTS (1u << 16)
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-// Arguments as citlali_attention_decode (api.h), without the scratch pointer and its size.
+// Arguments as citlali_attention_decode (api.h), without the scratch and counter pointers and their sizes.
 int citlali_attention_decode_no_alloc(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                       const int32_t* page_table, int page_table_stride,
                                       const int32_t* row_slot, const int32_t* row_pos,

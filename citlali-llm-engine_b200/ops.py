@@ -265,9 +265,11 @@ def attention_decode(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos,
     l.citlali_attention_decode_scratch_floats.restype = ctypes.c_size_t
     need = l.citlali_attention_decode_scratch_floats(_i(rows), _i(nq), _i(head_dim), _i(page_size), _i(max_positions))
     ws = _scratch(q.device, "attention_decode", need * 4)
+    counters = _scratch(q.device, "attention_decode counters", rows * nq * 4, zeroed=True)
     _check(l.citlali_attention_decode(
         _ptr(q), _i(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _i(page_table.shape[1]),
         _ptr(row_slot), _ptr(row_pos), _ptr(out), _i(out.shape[1]), _ptr(ws), ctypes.c_size_t(ws.numel() // 4),
+        _ptr(counters), ctypes.c_size_t(counters.numel() // 4),
         _i(rows), _i(nq), _i(nkv), _i(head_dim), _i(page_size), _i(window or 0), _i(max_positions), _f(scale),
         _stream()),
         # one kernel whose blocks merge through distributed shared memory, or a partial and a merge kernel
@@ -339,15 +341,16 @@ def gemm_tc_pair(x, w, y, accumulate=False, error_flag=None, swiglu=False):
                                       _ptr(error_flag), _stream()), "gemm_tc_pair")
 
 
-def _scratch(device, purpose: str, nbytes: int) -> torch.Tensor:
+def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.Tensor:
     """One scratch buffer per device and purpose (split-context attention partials, argmax segments);
-    it only grows.  Kernels on one stream use it one after another."""
+    it only grows.  Kernels on one stream use it one after another.  ``zeroed``: filled with zeros when it
+    is made (for counters that every kernel leaves at zero)."""
     key = (torch.device(device).index or 0, purpose)
     ws = _workspace.get(key)
     if ws is None or ws.numel() < nbytes:
         require(not torch.cuda.is_current_stream_capturing(),
                 f"the {purpose} scratch buffer would have to grow during graph capture; run the step once before capturing")
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = (torch.zeros if zeroed else torch.empty)(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
     return ws
 

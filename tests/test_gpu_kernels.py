@@ -551,6 +551,54 @@ def test_attention_decode_split_over_the_context(nq, nkv, d, page, window):
         assert (out[-1].view(nq, d)[0].double().cpu() - v[-1][7, 0]).abs().max() < 0.1
 
 
+@pytest.mark.parametrize("nq,nkv,d,window,scale_q8", [(8, 4, 128, 0, 256), (10, 2, 64, 0, 128), (4, 4, 32, 2000, 256), (40, 2, 16, 0, 64)])
+def test_attention_decode_many_rows_of_unequal_lengths(nq, nkv, d, window, scale_q8):
+    """Steps of so many rows that each (row, key/value head) gets one block: the pages of the rows that are much
+    longer than the mean are dealt to several blocks on the device (their results merged by the block that finishes
+    last), the others keep one.  Lengths from 1 to 3,000 in one step; a far key of the longest row takes all the
+    weight of one head; the same step twice (the counters are back at zero) and with another run length."""
+    import ctypes
+    g = torch.Generator().manual_seed(nq + d)
+    dtype, page = torch.bfloat16, 64
+    rows = -(-152 // (nkv * -(-(nq // nkv) // 16)))
+    rng = __import__("random").Random(d)
+    lengths = [rng.choice((1, 3, 64, 65, 130, 200, 511, 513)) for _ in range(rows - 3)] + [3000, 1500, 2049]
+    k = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lengths]
+    v = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lengths]
+    q = [(torch.randn(1, nq, d, generator=g) * 2).to(dtype).double() for n in lengths]
+    far = rows - 3
+    if window == 0:
+        q[far][0, :, 3] = 20.0; k[far][7, :, 3] = 20.0
+    kp, vp, table = make_paged(k, v, lengths, page, dtype, seed=3)
+    qrow = torch.cat([x.reshape(1, nq * d) for x in q]).to(dtype).to(DEV)
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    kd, vd, td = kp.to(DEV), vp.to(DEV), table.to(DEV)
+    lib = ops.lib()
+    outs = []
+    try:
+        for on, q8 in ((1, scale_q8), (1, scale_q8), (0, 256)):
+            lib.citlali_attention_decode_set_by_length(ctypes.c_int(on), ctypes.c_int(q8))
+            out = torch.full((rows, nq * d), float("nan"), dtype=dtype, device=DEV)
+            ops.attention_decode(qrow, nq * d, kd, vd, td, slots, pos, out, nq, nkv, d, page, window, table.shape[1] * page,
+                                 1.0 / math.sqrt(d))
+            outs.append(out)
+    finally:
+        lib.citlali_attention_decode_set_by_length(ctypes.c_int(1), ctypes.c_int(160))
+    assert torch.equal(outs[0], outs[1])                       # the counters came back to zero
+    assert not torch.equal(outs[0], outs[2])                   # and the long rows were in fact merged from several runs
+    short = [b for b, n in enumerate(lengths) if n <= 1024]      # at most the sixteen pages of the shortest run
+    assert torch.equal(outs[0][short], outs[2][short])         # rows that keep one block: the same arithmetic
+    for b, n in enumerate(lengths):
+        qfull = torch.cat([torch.zeros(n - 1, nq, d, dtype=torch.float64), q[b]])
+        want = plain.causal_attention(qfull, k[b], v[b], nq, nkv, window=window or None)[-1]
+        for out in (outs[0], outs[2]):
+            err = float((out[b].view(nq, d).double().cpu() - want).abs().max())
+            assert err <= 2 ** -8 * float(want.abs().max()), f"sequence of {n}: |diff| {err:.3e}"
+    if window == 0:
+        assert (outs[0][far].view(nq, d)[0].double().cpu() - v[far][7, 0]).abs().max() < 0.1
+
+
 def test_attention_decode_one_long_sequence():
     """One sequence of 8,400 tokens in a cache laid out for more than 8,192: the blocks of a head group are a
     cluster of sixteen.  A far key takes nearly all the weight of one head; with a window only its keys count."""
