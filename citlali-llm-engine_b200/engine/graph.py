@@ -105,27 +105,26 @@ class DecodeGraphRunner:
             ops.sample_rows(logits, self.floats[0], self.floats[1], self.out_tokens[:n])
         return logits
 
-    def _graph(self, n: int, greedy: bool) -> torch.cuda.CUDAGraph:
+    def _run(self, n: int, greedy: bool) -> None:
+        """Run the step whose inputs are in place: replay its graph, or, the first time a batch size is met, run it
+        with plain launches (which also sizes scratch buffers and sets kernel attributes) and capture the graph for
+        the steps to come.  A step is never run twice: a mixer's state of its own would be advanced twice."""
         key = (n, greedy)
         g = self.graphs.get(key)
         if g is not None:
-            return g
-        # run once outside capture: compiles nothing, but sizes scratch buffers and sets kernel attributes
-        side = torch.cuda.Stream(device=self.model.ctx.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            self._body(n, greedy)
-        torch.cuda.current_stream().wait_stream(side)
+            g.replay()
+            return
+        first = self._body(n, greedy)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(g, pool=self._pool):
             self.logits[key] = self._body(n, greedy)
         self.kernels_per_replay[key] = ops.launch_count() - before
+        self.logits[key].copy_(first)             # this step's logits, where later steps' logits will be found
         if self._pool is None:
             self._pool = g.pool()
         self.graphs[key] = g
-        return g
 
     def fill(self, slots: Sequence[int], tokens: Optional[Sequence[int]], positions: Sequence[int],
              temperature: float, uniforms: Sequence[float]) -> None:
@@ -163,10 +162,7 @@ class DecodeGraphRunner:
         for s, p in zip(slots, positions):
             self.cache.reserve(s, p + 1)
         self.fill(slots, tokens, positions, temperature, uniforms)
-        # the inputs are in place before a first capture: its trial run is then this very step,
-        # and running a step twice writes the same keys and values twice
-        g = self._graph(n, greedy)
-        g.replay()
+        self._run(n, greedy)
         for s, p in zip(slots, positions):
             self.cache.commit(s, p + 1)
         return self.kernels_per_replay[(n, greedy)]

@@ -34,7 +34,18 @@ class RunningMeanMixer:
         self.proj.bind(weights, ctx)
         self.dtype = ctx.dtype
 
+    # a step of single tokens finds its slots in the step's device tensors alone, so it can be captured in a graph
+    graph_safe = True
+
     def forward(self, h, batch, cache_view, residual, write_cache=True):
+        if batch.is_decode:
+            slots = batch.row_slot.long()
+            state = cache_view.storage.index_select(0, slots)
+            state[:, :-1] += h.float()
+            state[:, -1] += 1.0
+            cache_view.storage.index_copy_(0, slots, state)
+            self.proj.forward((state[:, :-1] / state[:, -1:]).to(self.dtype), accumulate_into=residual)
+            return residual
         means = torch.empty(h.shape, dtype=torch.float32, device=h.device)
         for b, slot in enumerate(batch.slots):
             state = cache_view.storage[slot]
@@ -281,6 +292,36 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, tmp_pa
         for (rid, pos), row in got.items():
             ref = want[rid][pos]
             assert (row.double() - ref).abs().max() <= tolerance * ref.abs().max() + 1e-6
+
+
+def test_toy_mixer_with_state_decodes_inside_a_replayed_graph(toy_registered, tmp_path):
+    """The toy mixer says it is graph-safe (its single-token path reads slots from the device), so the session
+    captures the decode step with the mixer's state updates inside: five requests over two slots (states are
+    zeroed when a slot is taken again) give the same tokens as plain launches, and the logits after a replayed
+    run still match the oracle."""
+    cfg = ToyConfig(vocab_size=300, hidden_size=64, max_position_embeddings=256)
+    folder = cb.write_random_model(str(tmp_path / "toy"), cfg, seed=3, dtype="bfloat16")
+    import random
+    rng = random.Random(9)
+    prompts = [[rng.randrange(300) for _ in range(n)] for n in (7, 40, 3, 19, 11)]
+    opts = cb.GenerationOptions(max_new_tokens=25, max_context=256, stop_ids=[])
+    session = cb.InferenceSession().load_model(folder, max_context=256, dtype="bfloat16", max_batch=2)
+    assert session.runner is not None
+    with_graph = [r.tokens for r in session.generate(prompts, opts)]
+    assert len(session.runner.graphs) > 0 and all(len(t) == 25 for t in with_graph)
+    plain_launches = cb.InferenceSession()
+    plain_launches.use_graphs = False
+    plain_launches.load_model(folder, max_context=256, dtype="bfloat16", max_batch=2)
+    assert plain_launches.runner is None
+    assert [r.tokens for r in plain_launches.generate(prompts, opts)] == with_graph
+    # the engine's own continuation, fed whole to the oracle: the last logits it saw are the oracle's
+    _, w = plain.load_folder(folder)
+    slot = session.acquire()
+    whole = prompts[1] + with_graph[1]
+    logits = session.step([cb.StepEntry(slot, whole, [len(whole) - 1])])[0]
+    session.release(slot)
+    ref = plain_toy(w, whole)[-1]
+    assert (logits.double().cpu() - ref).abs().max() <= 2.5e-2 * ref.abs().max()
 
 
 def test_unknown_part_kind_in_a_spec_is_an_error(tmp_path):
