@@ -581,10 +581,11 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
     int split = 1;
     for (int s = 8; s >= 2; s /= 2)
         if (pairs * s <= 300) { split = s; break; }
-    // One or few sequences in a cache laid out for long contexts (more than 8,192 tokens a sequence): a cluster of
-    // sixteen (not portable) a head group.  Measured at batch 1: 25 against 31 us at 16,000 cached tokens, 45
-    // against 56 at 32,000, but 7.8 against 5.9 at 500; the table's width, unlike the lengths, is fixed for a session.
-    if (pairs * 16 <= 128 && page_table_stride > 128) split = 16;
+    // One or few sequences in a cache laid out for more than 2,048 tokens a sequence: a cluster of sixteen (not
+    // portable) a head group.  Measured at batch 1, sixteen against eight blocks: 5.3 against 5.1 us at 1,000 cached
+    // tokens, 6.7 against 7.1 at 2,000, 8.3 against 9.6 at 4,000, 12.7 against 15.9 at 8,000, 25 against 31 at
+    // 16,000; the table's width, unlike the lengths, is fixed for a session.
+    if (pairs * 16 <= 128 && page_table_stride > 32) split = 16;
     if (g_forced_split > 0) split = g_forced_split > kMaxClusterBlocks ? kMaxClusterBlocks : g_forced_split;
     // Many rows (one block each would fill the GPU): the rows' lengths decide, on the device, which of them get
     // more than one block.  Needs the scratch for their partial results and the zeroed counters.
