@@ -138,6 +138,9 @@ int citlali_gemm_tc_normed(const void* x, const void* w, void* y, int y_dtype, i
 int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y_dtype, int M, int N, int K,
                          int mode, int32_t* error_flag, cudaStream_t stream);
 int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs);
+// Many rows: the row tiles run in bands whose rows of x (this many bytes, default 32 MiB) stay in L2 while all
+// weight tiles pass by.  Sets the size and returns the one before (for tuning).
+long citlali_gemm_tc_pair_set_band_bytes(long bytes);
 int citlali_gemm_tc_set_pair_rows(int rows);
 // The kernels' bounded wait on its own: a block waits `limit_ns` (at most one second) on a barrier on which
 // nothing arrives, gives up, records code 900 in error_flag[1] and its block in error_flag[2], and leaves

@@ -36,6 +36,7 @@ struct Params {
     int out_kind;
     int M, N, K;
     int32_t* error_flag;
+    int band;              // row tiles that are finished across all weight tiles before the next ones begin
 };
 
 template <int BN>
@@ -86,7 +87,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int kblocks = (p.K + kBK - 1) / kBK;
     const int units = tiles_m * tiles_n;
     const int pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    // unit -> (row tile, weight tile): the row tile runs fastest, so pairs that run together share a weight tile
+    // unit -> (row tile, weight tile): the row tile runs fastest, so pairs that run together share a weight tile.  Of a
+    // matrix of many rows (several prompts in a step) the row tiles are taken in bands of p.band: a band's rows of x
+    // are few enough to stay in L2 while all the weight tiles pass by, so x comes from memory once and the weights once
+    // a band; without bands every weight tile would bring all of x in again.
+    const int per_band = p.band * tiles_n;
+    auto unit_tiles = [&](int u, int& tm, int& tn) {
+        const int b = u / per_band, r = u - b * per_band;
+        const int rows_here = min(p.band, tiles_m - b * p.band);
+        tn = r / rows_here;
+        tm = b * p.band + (r - tn * rows_here);
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -95,7 +106,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t it = 0;
             bool ok = true;
             for (int u = pair_id; u < units && ok; u += pairs) {
-                const int tm = u % tiles_m, tn = u / tiles_m;
+                int tm, tn;
+                unit_tiles(u, tm, tn);
                 const int row_a = tm * 2 * kBM + (int)rank * kBM, row_b = tn * BN + (int)rank * (BN / 2);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
@@ -154,7 +166,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t leader_acc_empty0 = cluster_addr(smem_u32(&acc_empty_bar[0]), 0);
         uint32_t acc_it = 0;
         for (int u = pair_id; u < units; u += pairs, ++acc_it) {
-            const int tm = u % tiles_m, tn = u / tiles_m;
+            int tm, tn;
+            unit_tiles(u, tm, tn);
             const int as = acc_it % kAccStages;
             if (!mbar_wait(smem_u32(&acc_full_bar[as]), (acc_it / kAccStages) & 1u, abort_flag, p.error_flag, 304)) break;
             tc_fence_after();
@@ -252,6 +265,16 @@ static int launch(const void* x, const void* w, const Params& p, cudaStream_t st
 
 using namespace citlali;
 
+// Bytes of x (rows of a band of row tiles, all of K) that should stay in L2 while the weight tiles pass by.
+static long g_band_bytes = 32L << 20;
+
+// For tuning: sets the band's size in bytes and returns the one that stood before.
+extern "C" long citlali_gemm_tc_pair_set_band_bytes(long bytes) {
+    const long before = g_band_bytes;
+    if (bytes > 0) g_band_bytes = bytes;
+    return before;
+}
+
 // The tile width the pair kernel would use for this shape and how many pairs the device runs at once
 // (0: it does not run here).
 extern "C" int citlali_gemm_tc_pair_plan(int M, int N, int K, int* bn, int* pairs) {
@@ -290,6 +313,12 @@ extern "C" int citlali_gemm_tc_pair(const void* x, const void* w, void* y, int y
     }
     tc::pair::Params p;
     p.M = M; p.N = N; p.K = K;
+    {
+        const long tile_bytes = 2L * tc::pair::kBM * K * 2, tiles_m = (M + 2 * tc::pair::kBM - 1) / (2 * tc::pair::kBM);
+        long band = g_band_bytes / tile_bytes;
+        if (band < 4) band = 4;
+        p.band = (int)(band < tiles_m ? band : tiles_m);
+    }
     p.error_flag = error_flag;
     p.out = y;
     p.out_kind = swiglu ? tc::kSwigluBF16 : accumulate ? tc::kAddF32 : (y_dtype == kF32 ? tc::kStoreF32 : tc::kStoreBF16);

@@ -718,6 +718,34 @@ def test_gemm_tc_gate_epilogue(M, inter, K, one_block_or_pairs):
         ops.gemm_tc(x.to(DEV), packed[:2 * inter - 16].contiguous().to(DEV), torch.empty(M, inter - 8, dtype=torch.bfloat16, device=DEV), swiglu=True)
 
 
+def test_gemm_tc_on_pairs_of_sms_in_bands_of_row_tiles():
+    """Many rows: the row tiles are taken in bands (their rows of x stay in L2 while the weight tiles pass by).  With
+    bands of 4 row tiles (11 row tiles: bands of 4, 4 and 3) every tile is computed once and as without bands."""
+    import ctypes
+    M, N, K = 2700, 1100, 192
+    if ops.gemm_tc_pair_plan(M, N, K)["pairs"] == 0:
+        pytest.skip("this device runs no cluster of two blocks of that size")
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16); w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    xd, wd = x.to(DEV), w.to(DEV)
+    lib = ops.lib()
+    lib.citlali_gemm_tc_pair_set_band_bytes.restype = ctypes.c_long
+    whole = torch.full((M, N), 7.0, device=DEV)
+    ops.gemm_tc_pair(xd, wd, whole)                                     # default band: all 11 row tiles
+    before = lib.citlali_gemm_tc_pair_set_band_bytes(ctypes.c_long(1))
+    try:
+        banded = torch.full((M, N), -7.0, device=DEV)
+        ops.gemm_tc_pair(xd, wd, banded)
+        acc = torch.ones(M, N, device=DEV)
+        ops.gemm_tc_pair(xd, wd, acc, accumulate=True)                  # a tile done twice or never would show here
+    finally:
+        lib.citlali_gemm_tc_pair_set_band_bytes(ctypes.c_long(before))
+    assert torch.equal(banded, whole)
+    assert float((acc - 1.0 - whole).abs().max()) <= 1e-5 * float(want.abs().max())
+    assert float((whole.double().cpu() - want).abs().max()) <= 1e-5 * float(want.abs().max()) * 2
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (130, 144, 72), (1000, 1000, 512), (2048, 4096, 1024),
                                    (513, 96, 4096), (700, 1300, 2048), (2048, 4096, 4096)])
 def test_gemm_tc_on_pairs_of_sms(M, N, K):
