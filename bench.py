@@ -96,7 +96,7 @@ def workload_from_baseline(index):
                 decode_steps=num(r"then (\d+) decode steps"))
 
 
-def run_workload(index, repetitions):
+def run_workload(index, repetitions, layers=None):
     """One of BASELINE.json's batch workloads through ``InferenceSession.generate``: unequal prompts in
     one step, then the decode steps, host tokens in and out.  Prints one JSON line: decoded tokens a
     second (the median run), the prompts' tokens a second, and both against their rooflines."""
@@ -104,6 +104,9 @@ def run_workload(index, repetitions):
     import citlali_b200 as cb
 
     w = workload_from_baseline(index)
+    layers_full = w["num_hidden_layers"]
+    if layers:
+        w["num_hidden_layers"] = min(int(layers), layers_full)       # fewer layers of the same sizes (a profiler capture)
     context = -(-(w["longest"] + w["decode_steps"]) // cb.PAGE_SIZE) * cb.PAGE_SIZE
     cfg = cb.config_from_dict(dict(
         architectures=["Qwen3ForCausalLM"], num_hidden_layers=w["num_hidden_layers"], hidden_size=w["hidden_size"],
@@ -150,7 +153,7 @@ def run_workload(index, repetitions):
         "ms_per_step": decode_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
         "timing": "host clock around InferenceSession.generate's prompt step and decode steps, tokens from and to the host",
-        "config": {"model": w["name"], "layers": layers, "hidden": H, "q_heads": nq, "kv_heads": nkv, "head_dim": d,
+        "config": {"model": w["name"], "layers": layers, "layers_full": layers_full, "hidden": H, "q_heads": nq, "kv_heads": nkv, "head_dim": d,
                    "intermediate": I, "vocab": cfg.vocab_size, "global_batch": len(prompts), "prompt_tokens": tokens,
                    "shortest": min(map(len, prompts)), "longest": max(map(len, prompts)), "decode_steps": int(steps),
                    "repetitions": repetitions, "parallelism": "single GPU", "peaks": pk["source"]},
@@ -336,7 +339,7 @@ def main():
         return 2
 
     if args.workload != 2:
-        return run_workload(args.workload, max(1, args.repetitions))
+        return run_workload(args.workload, max(1, args.repetitions), args.layers)
 
     import torch
     import citlali_b200 as cb
