@@ -402,6 +402,23 @@ def main():
                "tflops": gemm_flops * per_s / 1e12, "repetitions": R}
     if "bf16_tflops_sustained" in pk:
         prefill["frac_sustained"] = gemm_flops * per_s / (pk["bf16_tflops_sustained"] * 1e12)
+    # The repetitions above follow one another at once and run under the power cap (about 1.5 GHz of 1.965 at 985 W);
+    # the burst peak is a short product's.  The same step alone, after 200 ms of rest, is what a single prompt costs.
+    rested = []
+    for i in range(R):
+        slot = session.acquire()
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        time.sleep(0.2)
+        a.record()
+        logits = session.step([cb.StepEntry(slot, prompt, [prefill_tokens - 1])])
+        session.sampler.sample_device(logits, 0.0, [])
+        b.record()
+        torch.cuda.synchronize()
+        session.release(slot)
+        rested.append(a.elapsed_time(b))
+    prefill["ms_after_rest"] = statistics.median(rested)
+    prefill["frac_after_rest"] = gemm_flops / (prefill["ms_after_rest"] / 1e3) / (pk["bf16_tflops"] * 1e12)
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---- decode: a run from the prompts' end to the context length, then the last steps again ----------
