@@ -195,3 +195,26 @@ def test_step_refuses_what_it_cannot_run(model_dirs):
         s.step([cb.StepEntry(a, [3], [0]), cb.StepEntry(a, [3], [0])])
     assert s.cache.length(a) == 2                              # refused steps changed nothing
     s.release(a); s.release(b)
+
+
+def test_a_batch_of_forty_requests_of_very_unequal_lengths(tmp_path):
+    """Forty requests decode together, three of them ten times longer than the rest: with one block a (row,
+    key/value head) the decode attention deals the long rows' pages to several blocks by length and merges their
+    results.  The batch, the long requests alone and the plain implementation agree."""
+    cfg = cb.config_from_dict(dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=128, num_attention_heads=8,
+                                   num_key_value_heads=4, head_dim=32, intermediate_size=208, vocab_size=600, rope_theta=1e4,
+                                   rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2048))
+    folder = cb.write_random_model(str(tmp_path / "forty"), cfg, 77, dtype="bfloat16")
+    pcfg, w = plain.load_folder(folder)
+    lengths = [20 + (37 * i) % 280 for i in range(37)] + [1500, 900, 1210]
+    reqs = [(f"q{i}", random_tokens(600, n, 900 + i)) for i, n in enumerate(lengths)]
+    want = {rid: plain.model_logits(pcfg, w, toks) for rid, toks in reqs}
+    s = cb.InferenceSession().load_model(folder, max_context=2048, dtype="bfloat16", max_batch=40)
+    prompt_lens = [len(t) - 6 for _, t in reqs]
+    together = replay.run_in_process(s, replay.batched(reqs, prompt_lens, 40))
+    check(together, want, "bfloat16", "forty together")
+    assert len(together) == 40 * 7
+    alone = replay.run_in_process(s, replay.batched(reqs[-3:], prompt_lens[-3:], 1))
+    for key, row in alone.items():
+        assert (row - together[key]).abs().max() <= TOL["bfloat16"] * together[key].abs().max()
+    assert s.cache.pages_held() == 0
