@@ -78,6 +78,7 @@ int citlali_attention_decode(const void* q, int q_stride, const void* k_pool, co
                              int max_positions, float scale, cudaStream_t stream);
 void citlali_attention_decode_set_split(int split);
 void citlali_attention_decode_set_by_length(int on, int run_scale_q8);
+void citlali_attention_decode_set_per_warp(int on);
 
 // Causal attention of runs of new tokens (bfloat16, pages of 64) on the tensor cores.  Sequence b
 // owns rows seq_start[b] .. seq_start[b+1]-1 at positions seq_past[b] + i of slot seq_slot[b].

@@ -273,7 +273,11 @@ constexpr int kMinRunTiles = 16;         // no run shorter than this many pages 
 // counters[row, head tile]; the block that counts last merges the runs in run order and puts the counter back to
 // zero.  Nobody waits for anybody.  Rows of about equal lengths keep one block each and nothing is merged.  The
 // number of runs depends on the lengths in the step, which are read on the device: the launch does not.
-template <int D, int kStagesKV, bool kByLength>
+//
+// kPerWarp (one or few rows: a block an SM at most, clusters of up to sixteen): a warp does not take its 16 keys of
+// every tile the block walks, with the block's two barriers a tile, but a run of 16-key units of its own, fetched into
+// a ring of its own (kStagesKV units) and waited for by the warp alone.  Nothing in the loop holds a warp up for another.
+template <int D, int kStagesKV, bool kByLength, bool kPerWarp = false>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                            const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
@@ -357,15 +361,51 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             cp_async_commit();
         }
     };
-    if (early) first_tiles();
+    // kPerWarp: units of 16 keys; the visible units are cut into split * 4 runs of equal length, this warp takes run
+    // rank * 4 + warp.  A unit's keys and values lie side by side in the warp's ring: [unit][keys | values].
+    constexpr int kUnitBytes = 16 * kRowBytes;
+    const int first_unit = lo >> 4, last_unit = pos >> 4;
+    const int per_warp = (last_unit - first_unit + split * 4) / (split * 4);
+    const int unit_lo = first_unit + (rank * 4 + warp) * per_warp, unit_hi = min(unit_lo + per_warp - 1, last_unit);
+    const int my_units = unit_hi - unit_lo + 1;                      // may be zero or less
+    const uint32_t ring = s_k + (uint32_t)warp * (kStagesKV * 2 * kUnitBytes);
+    auto load_unit = [&](int unit, int slot) {
+        const size_t base = (((size_t)pages[unit >> 2] * nkv + g) * kPage + (size_t)(unit & 3) * 16) * D;
+        const uint32_t dst = ring + (uint32_t)slot * (2 * kUnitBytes);
+        for (int c = lane; c < 16 * kChunksPerRow; c += 32) {
+            const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
+            const size_t src = base + (size_t)r * D + ch * 8;
+            cp_async16(dst + r * kRowBytes + ch * 16, k_pool + src);
+            cp_async16(dst + kUnitBytes + r * kRowBytes + ch * 16, v_pool + src);
+        }
+    };
+    if constexpr (kPerWarp) {
+        // every unit but the row's last holds keys and values of earlier steps only: fetched before the kernel ahead
+        // (which writes the new token's) has finished; the last unit, if it is among this warp's first, after it
+#pragma unroll
+        for (int i = 0; i < kStagesKV; ++i) {
+            if (i < my_units && unit_lo + i != last_unit) load_unit(unit_lo + i, i);
+            if (i < my_units && unit_lo + i == last_unit) break;    // its group is committed behind the wait, in order
+            cp_async_commit();
+        }
+    } else if (early) {
+        first_tiles();
+    }
     wait_for_predecessor();
+    if constexpr (kPerWarp) {
+        if (unit_hi == last_unit && my_units >= 1 && my_units <= kStagesKV) {
+            load_unit(last_unit, my_units - 1);
+#pragma unroll 1
+            for (int i = my_units - 1; i < kStagesKV; ++i) cp_async_commit();
+        }
+    }
     for (int c = tid; c < 16 * kChunksPerRow; c += 128) {
         const int r = c / kChunksPerRow, ch = c % kChunksPerRow;
         uint4 w = make_uint4(0, 0, 0, 0);
         if (r < heads_here) w = *reinterpret_cast<const uint4*>(q + (size_t)row * q_stride + (size_t)(head0 + r) * D + ch * 8);
         *reinterpret_cast<uint4*>(smem + r * kRowBytes + ch * 16) = w;
     }
-    if (!early) first_tiles();
+    if (!kPerWarp && !early) first_tiles();
 
     uint32_t qf[D / 16][4];
     __syncthreads();
@@ -381,13 +421,24 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
-    for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-        const int buf = (tile - tile_lo) % kStagesKV;
-        if (tile + kStagesKV - 1 <= tile_hi) load_tile(tile + kStagesKV - 1, (tile + kStagesKV - 1 - tile_lo) % kStagesKV);
-        cp_async_commit();
-        cp_async_wait<kStagesKV - 1>();
-        __syncthreads();
-        const uint32_t kb = s_k + buf * kTileBytes + warp * 16 * kRowBytes, vb = s_v + buf * kTileBytes + warp * 16 * kRowBytes;
+    const int steps = kPerWarp ? my_units : tile_hi - tile_lo + 1;
+    for (int step = 0; step < steps; ++step) {
+        const int tile = tile_lo + step;
+        uint32_t kb, vb;
+        if constexpr (kPerWarp) {
+            cp_async_wait<kStagesKV - 1>();
+            __syncwarp();
+            kb = ring + (uint32_t)(step % kStagesKV) * (2 * kUnitBytes);
+            vb = kb + kUnitBytes;
+        } else {
+            const int buf = step % kStagesKV;
+            if (tile + kStagesKV - 1 <= tile_hi) load_tile(tile + kStagesKV - 1, (step + kStagesKV - 1) % kStagesKV);
+            cp_async_commit();
+            cp_async_wait<kStagesKV - 1>();
+            __syncthreads();
+            kb = s_k + buf * kTileBytes + warp * 16 * kRowBytes;
+            vb = s_v + buf * kTileBytes + warp * 16 * kRowBytes;
+        }
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
 #pragma unroll
@@ -399,7 +450,7 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_16816(s[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
             mma_16816(s[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
         }
-        const int key_base = tile * kPage + warp * 16 + (lane & 3) * 2;
+        const int key_base = (kPerWarp ? (unit_lo + step) * 16 : tile * kPage + warp * 16) + (lane & 3) * 2;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int key = key_base + i * 8;
@@ -434,9 +485,16 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_16816(o[2 * np], p0, p1, p2, p3, b0, b1);
             mma_16816(o[2 * np + 1], p0, p1, p2, p3, b2, b3);
         }
-        __syncthreads();
+        if constexpr (kPerWarp) {
+            __syncwarp();                                             // the slot is free: the unit a ring's length on
+            if (step + kStagesKV < my_units) load_unit(unit_lo + step + kStagesKV, step % kStagesKV);
+            cp_async_commit();
+        } else {
+            __syncthreads();
+        }
     }
     cp_async_wait<0>();
+    if constexpr (kPerWarp) __syncthreads();                          // the parked rows lie over the other warps' rings
     // This block no longer reads its tile buffers: it says so to the cluster at once and waits for the others
     // only before it writes into theirs.
     if (!kByLength && split > 1) cluster_arrive();
@@ -534,10 +592,11 @@ attention_decode_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
 static int g_forced_split = 0;     // > 0: blocks per (sequence, head group), for tuning
 
+static int g_per_warp = 1;         // 0: never the kernel whose warps walk runs of their own
 static int g_run_scale_q8 = 160;   // by-length kernel: a run's length in 1/256 of the mean length of the step's rows
 static int g_by_length = 1;        // 0: never deal a row's pages out by length
 
-template <int D, int kStagesKV, bool kByLength = false>
+template <int D, int kStagesKV, bool kByLength = false, bool kPerWarp = false>
 static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, const void* v_pool, const int32_t* page_table,
                      int page_table_stride, const int32_t* row_slot, const int32_t* row_pos, void* out, int out_stride,
                      int rows, int nq, int nkv, int window, float scale, int split, cudaStream_t stream,
@@ -546,7 +605,7 @@ static int launch_tc_stages(const void* q, int q_stride, const void* k_pool, con
     // the query rows, the four warps' parked rows, and behind them what the cluster's blocks send (at most 31 runs)
     constexpr int park = 16 * (D * 2 + 16) + (4 * 16 + 32) * (D + 2) * 4;
     constexpr int smem = tiles > park ? tiles : park;
-    auto kernel = attention_decode_tc_kernel<D, kStagesKV, kByLength>;
+    auto kernel = attention_decode_tc_kernel<D, kStagesKV, kByLength, kPerWarp>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -598,8 +657,15 @@ static int launch_tc(const void* q, int q_stride, const void* k_pool, const void
                                                         row_pos, out, out_stride, rows, nq, nkv, window, scale, runs, stream,
                                                         partial, counters);
     }
-    // with at most one block per SM there is shared memory for six tiles in flight (head sizes up to 128)
+    // One or two rows (at most a block an SM): every warp walks a run of 16-key units of its own, three units in flight
+    // a warp.  Measured against the block-wide walk at batch 1: 8.1 against 8.5 us at 4,000 cached tokens, 11.5 against
+    // 13.5 at 8,000, 18.0 against 23.4 at 16,000 (batch 2: 10.8 / 12.5, 17.3 / 21.6, 30.3 / 39.7); with more rows, where
+    // the launch is bound by bandwidth, it gains nothing (batch 8 at 4,000: 23.9 either way).  A ring of six units a
+    // warp (one block an SM) lost 3.5 us at every length: the next launch's blocks no longer fit beside this one's.
     if constexpr (D <= 128) {
+        if (g_per_warp && pairs * split <= device_sm_count())
+            return launch_tc_stages<D, kKvStages, false, true>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, out,
+                                                       out_stride, rows, nq, nkv, window, scale, split, stream);
         if (pairs * split <= 80)          // more blocks than that, each filling an SM, no longer fit cluster by cluster
             return launch_tc_stages<D, 6>(q, q_stride, k_pool, v_pool, page_table, page_table_stride, row_slot, row_pos, out,
                                           out_stride, rows, nq, nkv, window, scale, split, stream);
@@ -648,6 +714,9 @@ extern "C" void citlali_attention_decode_set_split(int split) { g_forced_split =
 
 // Tuning of the kernel that deals a long row's pages out by length (steps of many rows): on/off, and a run's
 // length in 1/256 of the mean length of the step's rows (256: the mean itself; 0 leaves it as it is).
+// Tuning: 0 turns off the form for one or few rows in which every warp walks a run of 16-key units of its own.
+extern "C" void citlali_attention_decode_set_per_warp(int on) { g_per_warp = on; }
+
 extern "C" void citlali_attention_decode_set_by_length(int on, int run_scale_q8) {
     g_by_length = on;
     if (run_scale_q8 > 0) g_run_scale_q8 = run_scale_q8;
