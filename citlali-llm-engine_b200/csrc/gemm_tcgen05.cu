@@ -68,10 +68,12 @@ struct GemmParams {
 template <int BN>
 constexpr int stages_for(bool swapped) {
     // Swapped (few rows of x): two blocks per SM of about 100 KB each (one of 192 KB for tiles of 256 rows of
-    // x); up to 32 rows of x the split-K receive area (BN x 512 bytes) lies behind the ring, wider tiles
-    // reuse the ring for it.  Normal: one block of
+    // x); up to 64 rows of x the split-K receive area (BN x 512 bytes) lies behind the ring, wider tiles
+    // reuse the ring for it (and need a cluster barrier more).  For 64 rows that means three stages instead of
+    // four; measured on the four products of a layer: 14.2 / 10.6 / 40.0 / 21.2 us against 14.5 / 12.8 / 38.9 / 22.3.
+    // Normal: one block of
     // about 200 KB, and 20 KB behind the ring for the epilogue warps.
-    return swapped ? (BN <= 16 ? 5 : BN <= 64 ? 4 : BN <= 128 ? 3 : 4) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
+    return swapped ? (BN <= 16 ? 5 : BN <= 32 ? 4 : BN <= 128 ? 3 : 4) : (BN <= 128 ? 6 : BN <= 192 ? 5 : 4);
 }
 
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
@@ -114,7 +116,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Split K: where the other blocks of the cluster put their partial sums of this block's share of the
     // tile.  Behind the ring for narrow tiles; over the ring for wide ones, which then need a cluster
     // barrier between the last MMA of every block and the first partial sent.
-    constexpr bool kRecvInRing = BN >= 64;
+    constexpr bool kRecvInRing = BN >= 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t behind_ring = tiles + kStages * (kBytesA + kBytesB);
     const uint32_t recv = kRecvInRing ? tiles : behind_ring;
@@ -556,7 +558,7 @@ static Plan make_plan(int M, int N, int K, int sm_count, int force_splits = 0, b
 template <int BN, bool kSwapped>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
     constexpr int stages = stages_for<BN>(kSwapped);
-    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + (kSwapped ? (BN < 64 ? BN * 512 + 4096 : 0) : 8 * kEpilogueStageBytes) + 1024;      // ring, split-K receive area behind it, alignment
+    const size_t smem = (size_t)stages * (kBM * kBK * 2 + BN * kBK * 2) + (kSwapped ? (BN < 128 ? BN * 512 + 4096 : 0) : 8 * kEpilogueStageBytes) + 1024;      // ring, split-K receive area behind it, alignment
     auto kernel = gemm_tc_kernel<BN, kSwapped>;
     static bool configured = false;
     if (!configured) {

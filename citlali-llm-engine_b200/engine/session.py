@@ -13,6 +13,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..cache import PAGE_SIZE, SequenceCache
 from ..config.registry import config_from_model_dir
 from ..errors import CitlaliError, require
@@ -168,6 +169,7 @@ class InferenceSession:
             v = flag.tolist()
             if any(v):
                 flag.zero_()
+                ops.zero_counters()
                 raise CitlaliError(f"a kernel reported a fault: flag words {v}")
 
     # ---- generation ------------------------------------------------------------------------

@@ -341,6 +341,17 @@ def gemm_tc_pair(x, w, y, accumulate=False, error_flag=None, swiglu=False):
                                       _ptr(error_flag), _stream()), "gemm_tc_pair")
 
 
+_zeroed_purposes = set()
+
+
+def zero_counters() -> None:
+    """Put the scratch buffers that hold counters back to zero, in place (captured graphs keep their addresses).  For
+    after a kernel reported a fault: a step that gave up half-way may have left counters standing."""
+    for (index, purpose), ws in _workspace.items():
+        if purpose in _zeroed_purposes:
+            ws.zero_()
+
+
 def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.Tensor:
     """One scratch buffer per device and purpose (split-context attention partials, argmax segments);
     it only grows.  Kernels on one stream use it one after another.  ``zeroed``: filled with zeros when it
@@ -352,6 +363,8 @@ def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.T
                 f"the {purpose} scratch buffer would have to grow during graph capture; run the step once before capturing")
         ws = (torch.zeros if zeroed else torch.empty)(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
+        if zeroed:
+            _zeroed_purposes.add(purpose)
     return ws
 
 
