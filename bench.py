@@ -179,9 +179,10 @@ def run_reference(args):
     except Exception as e:
         return unavailable(f"baseline/reference_arm.py cannot be imported: {e}")
     why = reference_arm.installed()
-    if why and os.path.isdir("/root/reference"):
+    source = os.environ.get("CITLALI_REFERENCE_SOURCE", os.path.join(os.sep, "root", "reference"))    # a checkout of the reference, if one is at hand
+    if why and os.path.isdir(source):
         try:
-            reference_arm.install("/root/reference")
+            reference_arm.install(source)
             why = reference_arm.installed()
         except Exception as e:
             why = f"the reference could not be built here: {str(e)[-300:]}"
