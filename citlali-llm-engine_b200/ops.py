@@ -279,6 +279,7 @@ def attention_decode(q, q_stride, k_pool, v_pool, page_table, row_slot, row_pos,
 
 _sm_count = {}
 _workspace = {}
+_retired = []
 
 
 def sm_count(device) -> int:
@@ -361,6 +362,8 @@ def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.T
     if ws is None or ws.numel() < nbytes:
         require(not torch.cuda.is_current_stream_capturing(),
                 f"the {purpose} scratch buffer would have to grow during graph capture; run the step once before capturing")
+        if ws is not None:
+            _retired.append(ws)          # a captured graph may still hold its address: it is kept, not freed
         ws = (torch.zeros if zeroed else torch.empty)(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
         if zeroed:
