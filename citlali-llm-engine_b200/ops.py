@@ -351,6 +351,9 @@ def zero_counters() -> None:
     for (index, purpose), ws in _workspace.items():
         if purpose in _zeroed_purposes:
             ws.zero_()
+    for purpose, ws in _retired:
+        if purpose in _zeroed_purposes:
+            ws.zero_()
 
 
 def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.Tensor:
@@ -363,7 +366,7 @@ def _scratch(device, purpose: str, nbytes: int, zeroed: bool = False) -> torch.T
         require(not torch.cuda.is_current_stream_capturing(),
                 f"the {purpose} scratch buffer would have to grow during graph capture; run the step once before capturing")
         if ws is not None:
-            _retired.append(ws)          # a captured graph may still hold its address: it is kept, not freed
+            _retired.append((purpose, ws))          # a captured graph may still hold its address: it is kept, not freed
         ws = (torch.zeros if zeroed else torch.empty)(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspace[key] = ws
         if zeroed:
