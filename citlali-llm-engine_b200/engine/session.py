@@ -216,3 +216,16 @@ class InferenceSession:
         results = run_generation(self, prompts, opts, stops, batch, on_token)
         self.check_device_errors()
         return results
+
+    # The reference's session serves one sequence at a time under these names (include/citlali/runtime/session.h:40-45),
+    # with text in and out; here the same calls take and give token ids.
+    def generate_once_result(self, prompt: Sequence[int], options: Optional[GenerationOptions] = None,
+                             on_token: Optional[Callable[[int], None]] = None) -> GenerationResult:
+        """One sequence: its generated tokens, their number and why it stopped."""
+        each = (lambda index, token: on_token(token)) if on_token is not None else None
+        return self.generate([prompt], options, each)[0]
+
+    def generate_once(self, prompt: Sequence[int], options: Optional[GenerationOptions] = None,
+                      on_token: Optional[Callable[[int], None]] = None) -> List[int]:
+        """One sequence: its generated tokens."""
+        return self.generate_once_result(prompt, options, on_token).tokens

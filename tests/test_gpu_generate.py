@@ -64,6 +64,12 @@ def test_greedy_generation_matches_the_plain_loop(model_dirs, name, lengths, ste
     # one request alone gives the same tokens as in the batch
     alone = session.generate([prompts[1]], cb.GenerationOptions(max_new_tokens=steps, max_context=128, stop_ids=[]))
     assert alone[0].tokens == results[1].tokens
+    # the reference's names for one sequence
+    seen = []
+    once = session.generate_once_result(prompts[1], cb.GenerationOptions(max_new_tokens=steps, max_context=128, stop_ids=[]),
+                                        on_token=seen.append)
+    assert once.tokens == results[1].tokens == seen and once.generated_tokens == steps
+    assert session.generate_once(prompts[0], cb.GenerationOptions(max_new_tokens=3, max_context=128, stop_ids=[])) == results[0].tokens[:3]
 
 
 def test_head_sizes_the_single_token_kernel_refuses_step_without_graphs(tmp_path):
